@@ -1,0 +1,72 @@
+"""ctypes binding of the engine's CUDA library.
+
+Every entry point takes raw device pointers and the CUDA stream to launch on
+and allocates nothing; the wrappers here pass ``tensor.data_ptr()`` and the
+current torch stream.  There is no other implementation behind these names:
+if the library cannot be built or loaded, ``kernels()`` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+from . import build as _build
+
+_P = c_void_p
+_LIB: Optional[ctypes.CDLL] = None
+
+_SIGNATURES = {
+    "mf_embed": [_P, c_int, _P, _P, c_int, c_int, _P],
+    "mf_add_rmsnorm": [_P, _P, c_int, _P, c_float, _P, c_int, _P, c_int, c_int, _P],
+    "mf_rope_kv_write": [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, _P, _P, _P,
+                         _P, c_int, c_int, _P],
+    "mf_swiglu": [_P, _P, c_int, c_int, c_int, c_int, _P],
+    "mf_residual_add": [_P, _P, c_int, c_longlong, _P],
+    "mf_gemm_f32": [_P, _P, _P, c_int, c_int, c_int, c_int, _P],
+    "mf_attention_generic": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,
+                             c_float, c_int, _P],
+    "mf_sample": [_P, c_int, c_int, c_longlong, _P, _P, _P, _P],
+}
+
+MF_ERRORS = {10001: "a size or option this kernel does not take", 10002: "an unsupported dtype"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library() -> ctypes.CDLL:
+    """The loaded CUDA library; built on first use.  Raises if it cannot be had."""
+    global _LIB
+    if _LIB is None:
+        path = _build.library_path()
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"mlxforge_b200: cannot load its CUDA library {path}: {e}") from e
+        for name, args in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        _LIB = lib
+    return _LIB
+
+
+def declare(name: str, argtypes) -> None:
+    """Add the signature of a further entry point (used by kernel modules that
+    come with their own .cu file)."""
+    _SIGNATURES[name] = argtypes
+    if _LIB is not None:
+        fn = getattr(_LIB, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+
+
+def check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code in MF_ERRORS:
+        raise KernelError(f"{what}: refused: {MF_ERRORS[code]}")
+    import torch
+    raise KernelError(f"{what}: CUDA error {code} ({torch.cuda.cudart().cudaGetErrorString(code) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else ''})")

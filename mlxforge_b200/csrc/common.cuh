@@ -1,0 +1,80 @@
+// Shared helpers for the sm_100a kernels of mlxforge_b200.
+//
+// Conventions used by every entry point:
+//  * entry points are extern "C", take raw device pointers and the CUDA stream
+//    to launch on, allocate nothing, and return a cudaError_t code (0 = ok) or
+//    one of the MF_ERR_* codes below for an argument the kernel refuses;
+//  * `dtype` arguments are 0 for IEEE float32 and 1 for bfloat16;
+//  * matrices are row-major; weights are [out, in] as in the checkpoint.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MF_F32 0
+#define MF_BF16 1
+
+#define MF_ERR_BAD_ARG 10001      // a size the kernel does not take
+#define MF_ERR_BAD_DTYPE 10002
+
+#define MF_API extern "C" __attribute__((visibility("default")))
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum for blocks of up to 1024 threads; `red` is 32 floats of shared
+// memory.  Every thread gets the result.  The order of additions depends only on
+// the block size, never on what else runs.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = (lane < nw) ? red[lane] : 0.f;
+  r = warp_sum(r);
+  return r;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = (lane < nw) ? red[lane] : -INFINITY;
+  r = warp_max(r);
+  return r;
+}
+
+// Paged cache addressing.  One pool per cache lane (a layer's keys or values):
+// [page][kv_head][slot][head_dim].  `block_table` holds, per sequence of the
+// step, the page of every logical block; entries of blocks that were given back
+// (outside a window) are negative and are never addressed.
+struct PagedView {
+  const int* block_table;   // [n_seqs, bt_stride]
+  int bt_stride;
+  int page_size;
+  int n_kv_heads;
+  int head_dim;
+};
+__device__ __forceinline__ long long paged_offset(const PagedView& pv, int seq, int pos, int kv_head) {
+  const int blk = pos / pv.page_size, slot = pos - blk * pv.page_size;
+  const long long page = pv.block_table[(long long)seq * pv.bt_stride + blk];
+  return ((page * pv.n_kv_heads + kv_head) * pv.page_size + slot) * (long long)pv.head_dim;
+}

@@ -1,0 +1,113 @@
+"""Python-side launchers of the CUDA kernels, taking torch tensors.
+
+These are thin: they check what the kernel cannot check for itself, pass raw
+pointers and the current stream, and raise ``KernelError`` on a refusal.
+"""
+from __future__ import annotations
+
+from ctypes import c_void_p
+from typing import Optional
+
+import torch
+
+from .binding import KernelError, check, library
+
+F32, BF16 = 0, 1
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"tensor dtype {t.dtype} is neither float32 nor bfloat16")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise KernelError("kernel operands must be contiguous CUDA tensors "
+                              f"(got device={t.device}, contiguous={t.is_contiguous()})")
+
+
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
+    _need_cuda(table, tokens, out)
+    T, H = out.shape
+    check(library().mf_embed(table.data_ptr(), dtype_code(table), tokens.data_ptr(), out.data_ptr(), T, H,
+                             _stream()), "embed")
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    _need_cuda(resid, delta, weight, out, rows)
+    H = resid.shape[-1]
+    n = out.shape[0]
+    check(library().mf_add_rmsnorm(resid.data_ptr(), _ptr(delta), dtype_code(delta) if delta is not None else F32,
+                                   weight.data_ptr(), eps, out.data_ptr(), dtype_code(out), _ptr(rows), n, H,
+                                   _stream()), "add_rmsnorm")
+
+
+def residual_add(resid: torch.Tensor, delta: torch.Tensor) -> None:
+    _need_cuda(resid, delta)
+    check(library().mf_residual_add(resid.data_ptr(), delta.data_ptr(), dtype_code(delta), resid.numel(),
+                                    _stream()), "residual_add")
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                  block_table: torch.Tensor, page_size: int, freqs: Optional[torch.Tensor], q_out: torch.Tensor,
+                  k_pool: torch.Tensor, v_pool: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
+                  rotary_dim: int, write_kv: bool, precise: bool) -> None:
+    _need_cuda(qkv, positions, seq_of_token, block_table, freqs, q_out, k_pool, v_pool)
+    T = qkv.shape[0]
+    check(library().mf_rope_kv_write(qkv.data_ptr(), dtype_code(qkv), T, n_heads, n_kv, head_dim, rotary_dim,
+                                     positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
+                                     block_table.shape[1], page_size, _ptr(freqs), q_out.data_ptr(),
+                                     k_pool.data_ptr(), v_pool.data_ptr(), int(write_kv), int(precise),
+                                     _stream()), "rope_kv_write")
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int) -> None:
+    _need_cuda(gu, out)
+    T, I = out.shape
+    check(library().mf_swiglu(gu.data_ptr(), out.data_ptr(), dtype_code(gu), T, I, group, _stream()), "swiglu")
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    _need_cuda(a, w, out)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm_f32: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    check(library().mf_gemm_f32(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, int(accumulate),
+                                _stream()), "gemm_f32")
+
+
+def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                      positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                      page_size: int, n_heads: int, n_kv: int, head_dim: int, scale: float, window: int) -> None:
+    _need_cuda(q, k_pool, v_pool, out, positions, seq_of_token, block_table)
+    T = q.shape[0]
+    check(library().mf_attention_generic(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+                                         dtype_code(q), T, n_heads, n_kv, head_dim, positions.data_ptr(),
+                                         seq_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+                                         page_size, scale, window, _stream()), "attention_generic")
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], u: Optional[torch.Tensor],
+           out: torch.Tensor) -> None:
+    """Row r: argmax if temperature is None or temperature[r] <= 0, else an
+    inverse-CDF draw from softmax(logits[r] / temperature[r]) with u[r]."""
+    _need_cuda(temperature, u, out)
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 CUDA rows")
+    n, V = logits.shape
+    check(library().mf_sample(logits.data_ptr(), n, V, logits.stride(0), _ptr(temperature), _ptr(u),
+                              out.data_ptr(), _stream()), "sample")

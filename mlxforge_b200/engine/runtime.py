@@ -1,0 +1,64 @@
+"""What every part needs from the engine at run time: the compute dtype, the
+device, scratch buffers that are allocated once and reused by every step, and
+the matrix product (the one operation whose kernel depends on the dtype and on
+how many rows there are).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..csrc import ops
+
+
+class Runtime:
+    """``dtype`` float32 is the true 32-bit path (IEEE products on the CUDA cores,
+    angles in double); bfloat16 is the serving path (bfloat16 operands, 32-bit
+    accumulation, 32-bit residual stream, norms, softmax and logits)."""
+
+    def __init__(self, dtype: torch.dtype, device: str = "cuda"):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"compute dtype must be float32 or bfloat16, got {dtype}")
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.precise = dtype == torch.float32
+        self._buffers: Dict[str, torch.Tensor] = {}
+        # rows at or below which the bfloat16 product runs the skinny kernel
+        self.skinny_max_rows = 0
+
+    # ------------------------------------------------------------------ scratch
+    def buffer(self, name: str, shape: Tuple[int, ...], dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """A contiguous scratch tensor of ``shape``; the storage behind ``name``
+        only ever grows, so steady-state steps allocate nothing."""
+        dtype = dtype or self.dtype
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = f"{name}:{dtype}"
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf[:n].view(shape)
+
+    # ------------------------------------------------------------------ products
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """``out = x @ w^T`` with ``w`` [out_features, in_features].  float32
+        operands use this engine's IEEE kernel; bfloat16 operands use the skinny
+        kernel for few rows and the library product otherwise, accumulating in
+        32-bit and rounding once to ``out``'s dtype."""
+        if x.dtype == torch.float32 and w.dtype == torch.float32:
+            ops.gemm_f32(x, w, out)
+            return out
+        if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            raise ops.KernelError(f"linear: operand dtypes {x.dtype} x {w.dtype} are not a supported pair")
+        M = x.shape[0]
+        if M <= self.skinny_max_rows:
+            ops.skinny_linear(x, w, out)
+            return out
+        if out.dtype == torch.bfloat16:
+            torch.mm(x, w.t(), out=out)
+        else:
+            torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+        return out

@@ -1,0 +1,200 @@
+"""The step function: one flat batch of (request, its next tokens) — portions of
+prompts beside single decoded tokens, cut anywhere — run from the cache, with
+logits returned only at the places that were asked for.
+
+The reference never mixes the two kinds of work: a prefill chunk is a left-padded
+rectangle ``(B, L)`` and a decode step is ``(bucket, 1)`` with dummy rows, run
+back to back (src/runtime/worker.cpp:263-268,375-402,516-561;
+doc/architecture.md:123-125), and it computes logits for every position and
+slices afterwards (src/runtime/batching.cpp:46-49).  Here there are no padding
+rows and no buckets: ``T`` tokens of ``R`` sequences, each token with its own
+position and sequence index, and a block table per sequence and cache group.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, KVLane
+from ..cache.pages import SequenceCache
+from ..csrc import ops
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places among them
+    whose logits are wanted."""
+
+    seq: SequenceCache
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepBatch:
+    """Device-side description of one step, as every part sees it.
+
+    Tokens are laid out sequence after sequence; sequences that bring one token
+    (decoding) come first.  ``positions[t]`` is the token's index in its
+    sequence, ``seq_of_token[t]`` the row of its sequence in the block tables and
+    in ``slots``."""
+
+    def __init__(self):
+        self.n_tokens = 0
+        self.n_seqs = 0
+        self.n_wanted = 0
+        self.n_decode = 0                 # leading sequences (and tokens) that bring one token
+        self.tokens = None
+        self.positions = None
+        self.seq_of_token = None
+        self.want_rows = None
+        self.slots = None                 # [R] int32, device: state slot of every sequence
+        self.q_start: List[int] = []      # host copies, per sequence
+        self.q_len: List[int] = []
+        self.ctx_len: List[int] = []      # length after this step
+        self.slot_ids: List[int] = []
+        self.seq_q_start = None           # [R] device copies of the three lists
+        self.seq_q_len = None
+        self.seq_ctx_len = None
+        self._block_tables: Dict[int, torch.Tensor] = {}
+        self.max_ctx = 0
+        self.runner = None
+
+    def block_table(self, group: int) -> torch.Tensor:
+        return self._block_tables[group]
+
+    def attention(self, q, lane: KVLane, out, n_heads: int, scale: float, window: int) -> None:
+        """Attention of this step's queries over ``lane``; the kernel is chosen by
+        dtype and by how many tokens each sequence brings."""
+        self.runner.attention(self, q, lane, out, n_heads, scale, window)
+
+
+class ModelRunner:
+    """Owns the model, its cache manager and the step function."""
+
+    def __init__(self, model, cache: CacheManager, runtime):
+        self.model = model
+        self.cache = cache
+        self.rt = runtime
+        self.vocab = model.spec.vocab_size
+        self._pinned: Optional[torch.Tensor] = None
+        self._meta: Optional[torch.Tensor] = None
+        self._copied = torch.cuda.Event()
+        self._copy_pending = False
+        self.steps = 0
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the entries as one batch.  Returns float32 logits ``[wanted, vocab]``
+        on the device in the order of the entries and of their ``want`` lists
+        (None if nothing is wanted).  The returned tensor is scratch that the
+        next step overwrites.  On ``OutOfPages`` nothing has changed."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return None
+        seen = set()
+        for e in entries:
+            if e.seq.closed:
+                raise RuntimeError(f"sequence {e.seq.seq_id} is closed")
+            if e.seq.seq_id in seen:
+                raise ValueError(f"sequence {e.seq.seq_id} appears twice in one step")
+            seen.add(e.seq.seq_id)
+            n = len(e.tokens)
+            for w in e.want:
+                if not (0 <= w < n):
+                    raise IndexError(f"want index {w} is outside the {n} tokens of its entry")
+            lo, hi = min(e.tokens), max(e.tokens)
+            if lo < 0 or hi >= self.vocab:
+                raise IndexError(f"token id {lo if lo < 0 else hi} is outside the vocabulary [0, {self.vocab})")
+        self.cache.reserve([(e.seq, len(e.tokens)) for e in entries])
+        batch = self._build(entries)
+        logits = self.model.forward(batch, self.cache)
+        for e in entries:
+            self.cache.commit(e.seq, len(e.tokens))
+        self.steps += 1
+        return logits
+
+    # ------------------------------------------------------------------ metadata
+    def _build(self, entries: Sequence[StepEntry]) -> StepBatch:
+        order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
+        R = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        b = StepBatch()
+        b.runner = self
+        b.n_seqs, b.n_tokens = R, T
+        tokens = np.empty(T, dtype=np.int32)
+        positions = np.empty(T, dtype=np.int32)
+        seq_of = np.empty(T, dtype=np.int32)
+        start_of_entry = [0] * R
+        t = 0
+        for row, i in enumerate(order):
+            e = entries[i]
+            n = len(e.tokens)
+            tokens[t:t + n] = e.tokens
+            positions[t:t + n] = np.arange(e.seq.length, e.seq.length + n, dtype=np.int32)
+            seq_of[t:t + n] = row
+            start_of_entry[i] = t
+            b.q_start.append(t)
+            b.q_len.append(n)
+            b.ctx_len.append(e.seq.length + n)
+            b.slot_ids.append(e.seq.slot)
+            if n == 1:
+                b.n_decode += 1
+            t += n
+        b.max_ctx = max(b.ctx_len)
+        want: List[int] = []
+        for i, e in enumerate(entries):
+            want.extend(start_of_entry[i] + w for w in e.want)
+        b.n_wanted = len(want)
+
+        tables = []
+        for g in range(len(self.cache.pools)):
+            width = max(1, max(len(entries[i].seq.blocks[g]) for i in order))
+            tab = np.full((R, width), -1, dtype=np.int32)
+            for row, i in enumerate(order):
+                blocks = entries[i].seq.blocks[g]
+                tab[row, :len(blocks)] = blocks
+            tables.append(tab)
+
+        parts = [tokens, positions, seq_of, np.asarray(want, dtype=np.int32),
+                 np.asarray(b.slot_ids, dtype=np.int32), np.asarray(b.q_start, dtype=np.int32),
+                 np.asarray(b.q_len, dtype=np.int32), np.asarray(b.ctx_len, dtype=np.int32)]
+        parts += [tab.reshape(-1) for tab in tables]
+        # every part starts on a 16-byte boundary
+        offsets, total = [], 0
+        for p in parts:
+            offsets.append(total)
+            total += (p.size + 3) // 4 * 4
+        self._ensure_meta(total)
+        if self._copy_pending:
+            self._copied.synchronize()
+        host = self._pinned.numpy()
+        for p, off in zip(parts, offsets):
+            host[off:off + p.size] = p
+        self._meta[:total].copy_(self._pinned[:total], non_blocking=True)
+        self._copied.record()
+        self._copy_pending = True
+        views = [self._meta[off:off + p.size] for p, off in zip(parts, offsets)]
+        (b.tokens, b.positions, b.seq_of_token, b.want_rows, b.slots, b.seq_q_start, b.seq_q_len,
+         b.seq_ctx_len) = views[:8]
+        for g, tab in enumerate(tables):
+            b._block_tables[g] = views[8 + g].view(tab.shape)
+        return b
+
+    def _ensure_meta(self, n: int) -> None:
+        if self._pinned is None or self._pinned.numel() < n:
+            if self._copy_pending:
+                self._copied.synchronize()
+                self._copy_pending = False
+            cap = max(4096, 2 * n)
+            self._pinned = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            self._meta = torch.empty(cap, dtype=torch.int32, device=self.rt.device)
+
+    # ------------------------------------------------------------------ attention dispatch
+    def attention(self, batch: StepBatch, q, lane: KVLane, out, n_heads: int, scale: float, window: int) -> None:
+        need = lane.need
+        ops.attention_generic(q, lane.k, lane.v, out, batch.positions, batch.seq_of_token,
+                              batch.block_table(lane.group), lane.page_size, n_heads, need.n_kv_heads,
+                              need.head_dim, scale, window)
