@@ -56,6 +56,28 @@ def load_model_dir(model_dir):
     return cfg, read_safetensors(os.path.join(model_dir, "model.safetensors"))
 
 
+# ----------------------------------------------------------------------------- rounding model
+
+ROUND = None
+"""None: everything in float64.  A function (e.g. ``round_bf16``): applied to every
+activation a 16-bit engine would store in 16 bits (normed inputs, projections,
+rotated queries and keys, probabilities, attention output, feed-forward
+intermediates and the deltas added to the residual stream; never the residual
+stream, the softmax sums or the logits).  The gap between the two runs of this
+same plain implementation is the noise floor of bfloat16 activations for a given
+model and prompt; the tests derive their bfloat16 tolerance from it."""
+
+
+def round_bf16(x):
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)) << np.uint32(16)
+    return r.view(np.float32).astype(np.float64)
+
+
+def _r(x):
+    return x if ROUND is None else ROUND(x)
+
+
 # ----------------------------------------------------------------------------- parts
 
 def rope_frequencies(cfg):
@@ -101,7 +123,7 @@ def rms_norm(x, w, eps):
     """``x * rsqrt(mean(x^2) + eps) * w`` over the last axis; the weight multiplies
     directly, no ``1 + w`` (src/model/decoder_model.cpp:206-208)."""
     ms = np.mean(x * x, axis=-1, keepdims=True)
-    return x / np.sqrt(ms + eps) * w
+    return _r(x / np.sqrt(ms + eps) * w)
 
 
 def project_qkv(xn, wq, wk, wv, n_heads, n_kv_heads, head_dim):
@@ -109,9 +131,9 @@ def project_qkv(xn, wq, wk, wv, n_heads, n_kv_heads, head_dim):
     head ``h`` is output rows ``[h*hd, (h+1)*hd)`` (src/model/decoder_model.cpp:174-192,234-253).
     Returns q [nh, T, hd], k [nkv, T, hd], v [nkv, T, hd]."""
     T = xn.shape[0]
-    q = (xn @ wq.T).reshape(T, n_heads, head_dim).transpose(1, 0, 2)
-    k = (xn @ wk.T).reshape(T, n_kv_heads, head_dim).transpose(1, 0, 2)
-    v = (xn @ wv.T).reshape(T, n_kv_heads, head_dim).transpose(1, 0, 2)
+    q = _r(xn @ wq.T).reshape(T, n_heads, head_dim).transpose(1, 0, 2)
+    k = _r(xn @ wk.T).reshape(T, n_kv_heads, head_dim).transpose(1, 0, 2)
+    v = _r(xn @ wv.T).reshape(T, n_kv_heads, head_dim).transpose(1, 0, 2)
     return q, k, v
 
 
@@ -125,7 +147,7 @@ def apply_rope(x, positions, freqs):
     ang = np.asarray(positions, dtype=np.float64)[:, None] / freqs.astype(np.float64)[None, :]
     c, s = np.cos(ang), np.sin(ang)
     x1, x2 = x[..., :half], x[..., half:]
-    return np.concatenate([x1 * c - x2 * s, x1 * s + x2 * c], axis=-1)
+    return _r(np.concatenate([x1 * c - x2 * s, x1 * s + x2 * c], axis=-1))
 
 
 def attention(q, k, v, scale, window=0):
@@ -148,17 +170,16 @@ def attention(q, k, v, scale, window=0):
         s = np.where(visible, s, -np.inf)
         s = s - s.max(axis=-1, keepdims=True)
         p = np.exp(s)
-        p /= p.sum(axis=-1, keepdims=True)
-        out[:, h, :] = p @ v[h // rep]
-    return out.reshape(T, nh * hd)
+        out[:, h, :] = (_r(p) @ v[h // rep]) / p.sum(axis=-1, keepdims=True)
+    return _r(out.reshape(T, nh * hd))
 
 
 def swiglu_mlp(x, w_gate, w_up, w_down):
     """``down( silu(gate(x)) * up(x) )``, ``silu(g) = g * sigmoid(g)``
     (src/model/decoder_model.cpp:277-282)."""
-    g = x @ w_gate.T
-    u = x @ w_up.T
-    return ((g / (1.0 + np.exp(-g))) * u) @ w_down.T
+    g = _r(x @ w_gate.T)
+    u = _r(x @ w_up.T)
+    return _r(_r((g / (1.0 + np.exp(-g))) * u) @ w_down.T)
 
 
 def decoder_block(h, w, cfg, layer, positions, freqs, window=0):
@@ -174,7 +195,7 @@ def decoder_block(h, w, cfg, layer, positions, freqs, window=0):
     q = apply_rope(q, positions, freqs)
     k = apply_rope(k, positions, freqs)                       # v is never rotated
     a = attention(q, k, v, 1.0 / np.sqrt(hd), window)         # scale 1/sqrt(hd): decoder_model.cpp:265
-    h = h + a @ w[p + "self_attn.o_proj.weight"].T            # :273-274,290
+    h = h + _r(a @ w[p + "self_attn.o_proj.weight"].T)        # :273-274,290
     xn = rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
     return h + swiglu_mlp(xn, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                           w[p + "mlp.down_proj.weight"])

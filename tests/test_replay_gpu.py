@@ -12,9 +12,14 @@ from helpers import TINY, make_tiny, random_prompt
 pytestmark = pytest.mark.gpu
 
 # Tolerances.  float32: the engine differs from float64 by rounding only; logits of
-# these models are O(0.1 .. 1).  bfloat16: weights are exact in bfloat16, so the gap
-# is the rounding of activations (2^-9 relative each) through a few layers.
-TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+# these models are O(0.1 .. 1), so 1e-4 absolute (scaled up if a model's logits are
+# larger).  bfloat16: the weights are exact in bfloat16, so the gap is the rounding of
+# activations; its size depends on the model (a peaked softmax amplifies it), so it is
+# measured, per model, as the gap the plain implementation opens against itself when
+# it rounds its own activations to bfloat16 (plain_llama.ROUND), and the engine may
+# be three times that far from the float64 result.
+TOL_F32 = 1e-4
+BF16_NOISE_FACTOR = 3.0
 
 LENGTHS = {"A": [5, 17, 31, 70], "B": [1, 9, 40, 70, 131], "C": [3, 33, 64, 97]}
 
@@ -32,7 +37,15 @@ def models(tmp_path_factory):
             d, cfg, w = make_tiny(tmp, which, "bfloat16", qk_gain=gain)
             reqs = _requests(cfg, which)
             expected = {rid: P.forward_logits(cfg, w, toks) for rid, toks in reqs.items()}
-            out[(which, gain)] = (d, cfg, reqs, expected)
+            P.ROUND = P.round_bf16
+            try:
+                noise = max(float(np.max(np.abs(P.forward_logits(cfg, w, toks) - expected[rid])))
+                            for rid, toks in reqs.items())
+            finally:
+                P.ROUND = None
+            scale = max(float(np.max(np.abs(e))) for e in expected.values())
+            tol = {"float32": TOL_F32 * max(1.0, scale), "bfloat16": BF16_NOISE_FACTOR * noise}
+            out[(which, gain)] = (d, cfg, reqs, expected, tol)
     return out
 
 
@@ -62,21 +75,20 @@ MODES = {
 @pytest.mark.parametrize("gain", [1.0, 12.0])
 @pytest.mark.parametrize("which", list(TINY))
 def test_replay_matches_plain(models, tmp_path, which, gain, mode, dtype):
-    d, cfg, reqs, expected = models[(which, gain)]
+    d, cfg, reqs, expected, tols = models[(which, gain)]
     trace = MODES[mode](reqs)
     out_dir = _replay(d, dtype, trace, tmp_path)
     got = TT.read_outputs(trace, out_dir, cfg["vocab_size"])
     assert got, "the trace asked for nothing"
-    scale = max(float(np.max(np.abs(e))) for e in expected.values())
-    tol = TOL[dtype] * max(1.0, scale)
+    tol = tols[dtype]
     d_max, where = TT.worst(got, expected)
     assert d_max <= tol, (f"{which} gain {gain} {mode} {dtype}: max abs diff {d_max:.3e} at {where}, "
-                          f"first beyond tolerance at {TT.first_bad(got, expected, tol)}, logits scale {scale:.3f}")
+                          f"first beyond tolerance {tol:.3e} at {TT.first_bad(got, expected, tol)}")
 
 
 def test_mixed_reuses_pages(models, tmp_path):
     """The mixed trace runs far more tokens through the pool than it holds."""
-    d, cfg, reqs, expected = models[("B", 12.0)]
+    d, cfg, reqs, expected, tols = models[("B", 12.0)]
     trace = TT.mixed(reqs, max_live=2, seed=3)
     budget = trace.live_tokens_rounded()
     total = sum(len(t) for t in reqs.values())
@@ -84,4 +96,4 @@ def test_mixed_reuses_pages(models, tmp_path):
     out_dir = _replay(d, "float32", trace, tmp_path, max_tokens=budget)
     got = TT.read_outputs(trace, out_dir, cfg["vocab_size"])
     d_max, where = TT.worst(got, expected)
-    assert d_max <= 1e-4 * max(1.0, max(float(np.max(np.abs(e))) for e in expected.values())), (d_max, where)
+    assert d_max <= tols["float32"], (d_max, where)
