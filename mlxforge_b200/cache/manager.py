@@ -182,6 +182,13 @@ class CacheManager:
     def free_pages(self) -> List[int]:
         return [p.n_free for p in self.pools]
 
+    def total_pages(self) -> List[int]:
+        return [p.n_pages for p in self.pools]
+
+    def pages_for_tokens(self, n_tokens: int) -> List[int]:
+        """Pages per group that a new request of ``n_tokens`` takes."""
+        return [(n_tokens + self.page_size - 1) // self.page_size for _ in self.pools]
+
     def free_tokens(self) -> int:
         """Tokens that the tightest group can still take (whole pages)."""
         if not self.pools:

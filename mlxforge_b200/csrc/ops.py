@@ -111,3 +111,45 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], u: Optiona
     n, V = logits.shape
     check(library().mf_sample(logits.data_ptr(), n, V, logits.stride(0), _ptr(temperature), _ptr(u),
                               out.data_ptr(), _stream()), "sample")
+
+
+def apply_penalties(logits: torch.Tensor, params, histories) -> None:
+    """Repetition / frequency / presence penalties, in place, over each row's
+    history.  The unique ids and their counts are made on the host (the history
+    lives there) and sent in one copy."""
+    import numpy as np
+    n = logits.shape[0]
+    ids, counts, off = [], [], [0]
+    for r in range(n):
+        h = np.asarray(histories[r] if params[r].has_penalties else (), dtype=np.int64)
+        added = 0
+        if h.size:
+            u, c = np.unique(h, return_counts=True)
+            ids.append(u.astype(np.int32))
+            counts.append(c.astype(np.int32))
+            added = u.size
+        off.append(off[-1] + added)
+    if off[-1] == 0:
+        return
+    ints = np.concatenate(ids + counts + [np.asarray(off, dtype=np.int32)])
+    floats = np.asarray([[p.repetition_penalty for p in params], [p.frequency_penalty for p in params],
+                         [p.presence_penalty for p in params]], dtype=np.float32)
+    di = torch.from_numpy(ints).to(logits.device)
+    df = torch.from_numpy(floats).to(logits.device)
+    m = off[-1]
+    check(library().mf_apply_penalties(logits.data_ptr(), n, logits.stride(0), di[:m].data_ptr(),
+                                       di[m:2 * m].data_ptr(), di[2 * m:].data_ptr(), df[0].data_ptr(),
+                                       df[1].data_ptr(), df[2].data_ptr(), _stream()), "apply_penalties")
+
+
+def filter_logits(logits: torch.Tensor, params) -> None:
+    """top-k, top-p and min-p of every non-greedy row, in place (removed entries -inf)."""
+    import numpy as np
+    n, V = logits.shape
+    floats = np.asarray([[0.0 if p.greedy else p.temperature for p in params], [p.top_p for p in params],
+                         [p.min_p for p in params]], dtype=np.float32)
+    ks = np.asarray([p.top_k for p in params], dtype=np.int32)
+    df = torch.from_numpy(floats).to(logits.device)
+    dk = torch.from_numpy(ks).to(logits.device)
+    check(library().mf_filter_logits(logits.data_ptr(), n, V, logits.stride(0), df[0].data_ptr(), dk.data_ptr(),
+                                     df[1].data_ptr(), df[2].data_ptr(), _stream()), "filter_logits")

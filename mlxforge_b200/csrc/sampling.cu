@@ -106,3 +106,153 @@ MF_API int mf_sample(const float* logits, int n, int V, long long row_stride, co
   sample_kernel<<<n, SAMPLE_THREADS, 0, stream>>>(logits, V, row_stride, temperature, u, out);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------ penalties
+// Row r owns unique history ids[off[r] .. off[r+1]) with their counts.  For a seen
+// token: repetition divides a positive logit and multiplies a negative one, then
+// frequency subtracts penalty * count and presence subtracts penalty once
+// (src/sample/sampler.cpp:95-135).
+__global__ void penalties_kernel(float* __restrict__ logits, long long row_stride, const int* __restrict__ ids,
+                                 const int* __restrict__ counts, const int* __restrict__ off,
+                                 const float* __restrict__ rep, const float* __restrict__ freq,
+                                 const float* __restrict__ pres) {
+  const int r = blockIdx.x;
+  float* x = logits + (long long)r * row_stride;
+  const float rp = rep[r], fq = freq[r], pr = pres[r];
+  for (int i = off[r] + threadIdx.x; i < off[r + 1]; i += blockDim.x) {
+    const int id = ids[i];
+    float v = x[id];
+    if (rp != 1.0f) v = v > 0.f ? v / rp : v * rp;
+    v -= fq * (float)counts[i];
+    v -= pr;
+    x[id] = v;
+  }
+}
+
+MF_API int mf_apply_penalties(float* logits, int n, long long row_stride, const int* ids, const int* counts,
+                              const int* off, const float* rep, const float* freq, const float* pres,
+                              cudaStream_t stream) {
+  if (n <= 0) return 0;
+  penalties_kernel<<<n, 256, 0, stream>>>(logits, row_stride, ids, counts, off, rep, freq, pres);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ top-k / top-p / min-p
+// In place: removed entries become -inf.  Applied to logits / temperature in the
+// reference's order (src/sample/sampler.cpp:63-93,159-163): top-k keeps values >= the
+// k-th largest; top-p keeps the shortest prefix in descending order whose
+// probability reaches p (a token stays while the mass before it is < p); min-p
+// keeps probabilities >= min_p * the largest.  Thresholds are found by an 8-bit
+// radix descent over an order-preserving integer image of the floats; entries
+// equal to a threshold are all kept.
+__device__ __forceinline__ unsigned ordered_key(float f) {
+  const unsigned u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_to_float(unsigned k) {
+  const unsigned u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+  return __uint_as_float(u);
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+filter_kernel(float* __restrict__ logits, int V, long long row_stride, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p) {
+  __shared__ float red[32];
+  __shared__ unsigned hist_n[256];
+  __shared__ float hist_m[256];
+  __shared__ unsigned s_prefix;
+  __shared__ unsigned s_remaining;
+  __shared__ float s_acc;
+  const int r = blockIdx.x, tid = threadIdx.x;
+  float* x = logits + (long long)r * row_stride;
+  const float temp = temperature[r];
+  if (!(temp > 0.f) || !isfinite(temp)) return;     // greedy rows are not filtered
+  const float inv_t = 1.0f / temp;
+  const int k = top_k[r];
+  const float p = top_p[r], mp = min_p[r];
+
+  // ---- top-k: the k-th largest value by radix select on counts
+  if (k > 0 && k < V) {
+    if (tid == 0) { s_prefix = 0u; s_remaining = (unsigned)k; }
+    __syncthreads();
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      for (int b = tid; b < 256; b += SAMPLE_THREADS) hist_n[b] = 0u;
+      __syncthreads();
+      const unsigned prefix = s_prefix;
+      const unsigned himask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+      for (int i = tid; i < V; i += SAMPLE_THREADS) {
+        const unsigned key = ordered_key(x[i]);
+        if ((key & himask) == prefix) atomicAdd(&hist_n[(key >> shift) & 255u], 1u);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned rem = s_remaining;
+        int b = 255;
+        for (; b > 0; b--) {
+          if (hist_n[b] >= rem) break;
+          rem -= hist_n[b];
+        }
+        s_prefix = prefix | ((unsigned)b << shift);
+        s_remaining = rem;
+      }
+      __syncthreads();
+    }
+    const float kth = key_to_float(s_prefix);
+    for (int i = tid; i < V; i += SAMPLE_THREADS)
+      if (x[i] < kth) x[i] = -INFINITY;
+    __syncthreads();
+  }
+
+  if (!(p < 1.0f) && !(mp > 0.f)) return;
+  // ---- max and normaliser of softmax(x / T) over what is left
+  float mx = -INFINITY;
+  for (int i = tid; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, x[i]);
+  mx = block_max(mx, red);
+  if (p < 1.0f) {
+    float z = 0.f;
+    for (int i = tid; i < V; i += SAMPLE_THREADS) z += expf((x[i] - mx) * inv_t);
+    z = block_sum(z, red);
+    const float target = p * z;
+    if (tid == 0) { s_prefix = 0u; s_acc = 0.f; }
+    __syncthreads();
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      for (int b = tid; b < 256; b += SAMPLE_THREADS) hist_m[b] = 0.f;
+      __syncthreads();
+      const unsigned prefix = s_prefix;
+      const unsigned himask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+      for (int i = tid; i < V; i += SAMPLE_THREADS) {
+        const float v = x[i];
+        const unsigned key = ordered_key(v);
+        if ((key & himask) == prefix) atomicAdd(&hist_m[(key >> shift) & 255u], expf((v - mx) * inv_t));
+      }
+      __syncthreads();
+      if (tid == 0) {
+        float acc = s_acc;       // mass of everything strictly above the current prefix range
+        int b = 255;
+        for (; b > 0; b--) {
+          if (acc + hist_m[b] >= target) break;
+          acc += hist_m[b];
+        }
+        s_prefix = prefix | ((unsigned)b << shift);
+        s_acc = acc;
+      }
+      __syncthreads();
+    }
+    const float cut = key_to_float(s_prefix);
+    for (int i = tid; i < V; i += SAMPLE_THREADS)
+      if (x[i] < cut) x[i] = -INFINITY;
+    __syncthreads();
+  }
+  if (mp > 0.f) {
+    for (int i = tid; i < V; i += SAMPLE_THREADS)
+      if (expf((x[i] - mx) * inv_t) < mp) x[i] = -INFINITY;
+  }
+}
+
+MF_API int mf_filter_logits(float* logits, int n, int V, long long row_stride, const float* temperature,
+                            const int* top_k, const float* top_p, const float* min_p, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (V <= 0) return MF_ERR_BAD_ARG;
+  filter_kernel<<<n, SAMPLE_THREADS, 0, stream>>>(logits, V, row_stride, temperature, top_k, top_p, min_p);
+  return (int)cudaGetLastError();
+}

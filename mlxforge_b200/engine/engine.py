@@ -1,0 +1,218 @@
+"""The engine facade and its worker loop: the Python entry point.
+
+Shape of the reference's surface (src/runtime/engine.h:25-117, src/capi/mlxforge.h:169-323):
+an ``EngineConfig`` whose invalid combinations fail creation instead of falling
+back, ``submit`` that returns a request handle, ``request.next()`` that yields
+token ids until the request ends, ``cancel``, ``finish_reason``, ``metrics``,
+``stop`` that completes in-flight requests.  It is token-id based (tokenizers
+are out of scope) and in-process Python instead of a C ABI.
+
+One loop iteration = one scheduler plan, one step of the model over a mixed
+batch, one sampling call, one commit.  ``Engine.step()`` runs it on the caller's
+thread; ``Engine.start()`` runs the same loop on a worker thread, as the
+reference's single GPU thread does (src/runtime/worker.cpp:196-280).
+"""
+from __future__ import annotations
+
+import json
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pages import OutOfPages
+from ..sampling.params import GREEDY, SamplingParams
+from ..sampling.sampler import Sampler
+from .loading import load_model, parse_dtype
+from .request import FINISH_ERROR, Request
+from .scheduler import PlannedEntry, Scheduler, SchedulerConfig
+from .step import ModelRunner, StepEntry
+
+
+class QueueFull(RuntimeError):
+    pass
+
+
+@dataclass
+class EngineConfig:
+    """Options of an engine.  Names follow the reference where it has them
+    (``model_spec``, ``max_waiting``, ``kv_block_size``, ``kv_pool_bytes``,
+    ``prefill_chunk``, ``skinny_mm``, ``rope_scaling``; src/runtime/engine.h:25-67)."""
+
+    model_spec: str = ""
+    dtype: str = "bfloat16"            # "bfloat16" | "float32"
+    max_waiting: int = 256
+    kv_block_size: int = 16            # tokens per cache page
+    kv_pool_bytes: int = 1 << 30       # bytes of keys and values over all layers
+    kv_pool_tokens: int = 0            # > 0: size the pool in tokens instead
+    max_running: int = 64
+    token_budget: int = 2048
+    prefill_chunk: int = 512
+    skinny_mm: bool = True             # few-row products by the skinny kernel
+    cuda_graphs: bool = True           # replay decode-only steps from captured graphs
+    rope_scaling: str = ""             # JSON object replacing the checkpoint's rope_scaling
+
+    def validate(self) -> None:
+        if not self.model_spec:
+            raise ValueError("EngineConfig: model_spec (a folder with config.json) is required")
+        if self.kv_block_size <= 0 or self.kv_block_size % 16:
+            raise ValueError(f"EngineConfig: kv_block_size must be a positive multiple of 16, got {self.kv_block_size}")
+        if self.prefill_chunk <= 0 or self.token_budget <= 0:
+            raise ValueError("EngineConfig: prefill_chunk and token_budget must be positive")
+        if self.max_running <= 0 or self.max_waiting <= 0:
+            raise ValueError("EngineConfig: max_running and max_waiting must be positive")
+        if self.kv_pool_tokens <= 0 and self.kv_pool_bytes <= 0:
+            raise ValueError("EngineConfig: give kv_pool_bytes or kv_pool_tokens")
+        parse_dtype(self.dtype)
+
+
+class Engine:
+    def __init__(self, config: Optional[EngineConfig] = None, **kw):
+        if config is None:
+            config = EngineConfig(**kw)
+        elif kw:
+            raise TypeError("give either an EngineConfig or keyword options")
+        config.validate()
+        self.config = config
+        dtype = parse_dtype(config.dtype)
+        self.model, self.model_config = load_model(config.model_spec, dtype,
+                                                   rope_scaling=config.rope_scaling or None)
+        rt = self.model.rt
+        rt.skinny_enabled = bool(config.skinny_mm)
+        elt = 4 if dtype == torch.float32 else 2
+        per_token = max(1, self.model.cache_layout.bytes_per_token(elt))
+        tokens = config.kv_pool_tokens if config.kv_pool_tokens > 0 else config.kv_pool_bytes // per_token
+        tokens = max(tokens, config.kv_block_size)
+        self.cache = CacheManager(self.model.cache_layout, page_size=config.kv_block_size, max_tokens=tokens,
+                                  max_seqs=config.max_running, dtype=dtype, device=str(rt.device))
+        self.runner = ModelRunner(self.model, self.cache, rt, cuda_graphs=config.cuda_graphs)
+        self.scheduler = Scheduler(self.cache, SchedulerConfig(
+            max_running=config.max_running, max_waiting=config.max_waiting,
+            token_budget=config.token_budget, prefill_chunk=config.prefill_chunk))
+        self.sampler = Sampler(rt.device)
+        self._lock = threading.Lock()
+        self._wake = threading.Condition(self._lock)
+        self._thread: Optional[threading.Thread] = None
+        self._stop = False
+        self._t_busy = 0.0
+
+    # ------------------------------------------------------------------ submit
+    @property
+    def eos_token_ids(self):
+        return tuple(self.model.spec.eos_token_ids)
+
+    def submit_ids(self, prompt_ids: Sequence[int], params: Optional[SamplingParams] = None,
+                   max_tokens: int = 64, eos_ids: Optional[Sequence[int]] = None) -> Request:
+        """Queue a request.  ``eos_ids`` None takes the model's; an empty list
+        disables EOS (the reference's bench does that, apps/mlxforge_cli.cpp:319).
+        Raises ``QueueFull`` when ``max_waiting`` requests are waiting."""
+        vocab = self.model.spec.vocab_size
+        for t in prompt_ids:
+            if not (0 <= int(t) < vocab):
+                raise ValueError(f"token id {t} is outside the vocabulary [0, {vocab})")
+        req = Request(prompt_ids, params or SamplingParams(), max_tokens,
+                      self.eos_token_ids if eos_ids is None else eos_ids)
+        with self._wake:
+            if not self.scheduler.submit(req):
+                raise QueueFull(f"{self.config.max_waiting} requests are already waiting")
+            self._wake.notify_all()
+        return req
+
+    # ------------------------------------------------------------------ the loop
+    def step(self) -> int:
+        """One iteration: plan, run, sample, commit.  Returns the number of tokens
+        the step ran (0 when there was nothing to do)."""
+        with self._lock:
+            entries = self.scheduler.plan()
+        if not entries:
+            return 0
+        t0 = time.perf_counter()
+        try:
+            step_entries = []
+            for e in entries:
+                ids = e.request.all_ids[e.start:e.start + e.count]
+                step_entries.append(StepEntry(e.request.seq, ids, [e.count - 1] if e.samples else []))
+            logits = self.runner.step(step_entries)
+            sampled: List[int] = []
+            if logits is not None:
+                rows = [e.request for e in entries if e.samples]
+                sampled = self.sampler.sample(logits, [r.params for r in rows],
+                                              [len(r.output_ids) for r in rows],
+                                              [r.all_ids if r.params.has_penalties else () for r in rows])
+        except Exception as exc:    # the step failed: no request can go on
+            with self._lock:
+                self.scheduler.fail_all(f"{type(exc).__name__}: {exc}")
+            raise
+        with self._lock:
+            self.scheduler.commit(entries, sampled)
+        self._t_busy += time.perf_counter() - t0
+        return sum(e.count for e in entries)
+
+    def run_until_idle(self) -> None:
+        while not self.scheduler.idle:
+            if self.step() == 0 and not self.scheduler.idle:
+                raise RuntimeError("scheduler made no progress with requests outstanding")
+
+    # ------------------------------------------------------------------ worker thread
+    def start(self) -> None:
+        if self._thread is not None:
+            return
+        self._stop = False
+        self._thread = threading.Thread(target=self._run, name="mlxforge-worker", daemon=True)
+        self._thread.start()
+
+    def _run(self) -> None:
+        torch.cuda.set_device(self.model.rt.device)
+        while True:
+            with self._wake:
+                while self.scheduler.idle and not self._stop:
+                    self._wake.wait(timeout=0.1)
+                if self._stop and self.scheduler.idle:
+                    return
+            try:
+                self.step()
+            except Exception:
+                if self._stop:
+                    return
+
+    def stop(self) -> None:
+        """Complete what is in flight, then end the worker (src/runtime/worker.cpp:191-194,231-233)."""
+        with self._wake:
+            self._stop = True
+            self._wake.notify_all()
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None
+
+    # ------------------------------------------------------------------ conveniences
+    def generate(self, prompts: Sequence[Sequence[int]], params: Optional[SamplingParams] = None,
+                 max_tokens: int = 64, eos_ids: Optional[Sequence[int]] = None) -> List[List[int]]:
+        """Token ids in, generated token ids out, for one prompt or a batch."""
+        single = len(prompts) > 0 and isinstance(prompts[0], int)
+        batch = [prompts] if single else list(prompts)
+        reqs = [self.submit_ids(p, params or GREEDY, max_tokens, eos_ids) for p in batch]
+        if self._thread is None:
+            self.run_until_idle()
+        outs = []
+        for r in reqs:
+            while not r.finished:
+                time.sleep(0.0005)
+            if r.finish_reason == FINISH_ERROR:
+                raise RuntimeError(r.error)
+            outs.append(list(r.output_ids))
+        return outs[0] if single else outs
+
+    def metrics(self) -> Dict[str, float]:
+        """Counters in the manner of src/runtime/metrics.h:9-27."""
+        m = self.scheduler.metrics
+        return {
+            "steps": m.steps, "decode_tokens": m.decode_tokens, "prompt_tokens": m.prompt_tokens,
+            "completed": m.completed, "preemptions": m.preemptions, "peak_running": m.peak_running,
+            "running": len(self.scheduler.running), "waiting": len(self.scheduler.waiting),
+            "pages_free": min(self.cache.free_pages()) if self.cache.pools else 0,
+            "pages_total": min(self.cache.total_pages()) if self.cache.pools else 0,
+            "busy_seconds": self._t_busy,
+        }

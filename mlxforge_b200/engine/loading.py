@@ -9,7 +9,10 @@ from typing import Tuple
 
 import torch
 
-from ..config.registry import config_from_dir, get_architecture
+import json
+
+from ..config.model_config import ConfigError, read_config_json
+from ..config.registry import config_from_json, get_architecture
 from ..models.decoder import DecoderModel
 from .runtime import Runtime
 
@@ -32,11 +35,24 @@ def require_gpu() -> None:
                            "There is no CPU fallback.")
 
 
-def load_model(model_dir: str, dtype="bfloat16", device: str = "cuda") -> Tuple[DecoderModel, object]:
+def load_model(model_dir: str, dtype="bfloat16", device: str = "cuda",
+               rope_scaling: str = None) -> Tuple[DecoderModel, object]:
+    """``rope_scaling``: a JSON object that replaces the checkpoint's
+    ``rope_scaling`` wholesale (src/core/config.cpp:282-300)."""
     require_gpu()
     from ..csrc.binding import library
     library()      # build or load the kernels now: fail before any weight is read
-    config = config_from_dir(model_dir)
+    j = read_config_json(model_dir)
+    if rope_scaling:
+        try:
+            o = json.loads(rope_scaling)
+        except json.JSONDecodeError as e:
+            raise ConfigError(f"invalid rope_scaling override JSON: {e}")
+        if not isinstance(o, dict):
+            raise ConfigError('rope_scaling override must be a JSON object, e.g. {"rope_type":"linear","factor":4.0}')
+        j = dict(j)
+        j["rope_scaling"] = o
+    config = config_from_json(j)
     arch = get_architecture(config.architecture)
     rt = Runtime(parse_dtype(dtype), device)
     model = DecoderModel(arch.build_spec(config), rt)

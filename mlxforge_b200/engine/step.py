@@ -74,8 +74,9 @@ class StepBatch:
 class ModelRunner:
     """Owns the model, its cache manager and the step function."""
 
-    def __init__(self, model, cache: CacheManager, runtime):
+    def __init__(self, model, cache: CacheManager, runtime, cuda_graphs: bool = False):
         self.model = model
+        self.cuda_graphs = cuda_graphs
         self.cache = cache
         self.rt = runtime
         self.vocab = model.spec.vocab_size

@@ -1,0 +1,1 @@
+from .params import GREEDY, SamplingParams, uniform_draw

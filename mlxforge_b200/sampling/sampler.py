@@ -1,0 +1,64 @@
+"""Token selection for the rows of one step, on the device.
+
+Order of operations as in the reference (src/sample/sampler.cpp:141-166):
+penalties over the request's history (they apply to greedy too), then
+``temperature <= 0`` → argmax, else ``logits / temperature``, top-k, top-p,
+min-p, and a categorical draw.  The draw uses one uniform number per row from
+``uniform_draw(seed, output index)``.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from ..csrc import ops
+from .params import SamplingParams, uniform_draw
+
+
+class Sampler:
+    def __init__(self, device, max_rows: int = 1024):
+        self.device = torch.device(device)
+        self._cap = 0
+        self._host = None
+        self._dev = None
+        self._out = None
+        self._ensure(max_rows)
+
+    def _ensure(self, n: int) -> None:
+        if n <= self._cap:
+            return
+        self._cap = max(n, 2 * self._cap)
+        self._host = torch.empty((2, self._cap), dtype=torch.float32, pin_memory=True)
+        self._dev = torch.empty((2, self._cap), dtype=torch.float32, device=self.device)
+        self._out = torch.empty(self._cap, dtype=torch.int32, device=self.device)
+        self._out_host = torch.empty(self._cap, dtype=torch.int32, pin_memory=True)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], indices: Sequence[int],
+               histories: Sequence[Sequence[int]] = ()) -> List[int]:
+        """One token for every row of ``logits`` [n, V] (float32, device).
+        ``indices[r]`` is the output index of row r's request (it selects the
+        draw); ``histories[r]`` the tokens its penalties look at."""
+        n = logits.shape[0]
+        if n == 0:
+            return []
+        self._ensure(n)
+        if any(p.has_penalties for p in params):
+            ops.apply_penalties(logits, params, histories)
+        all_greedy = all(p.greedy for p in params)
+        out = self._out[:n]
+        if all_greedy:
+            ops.sample(logits, None, None, out)
+        else:
+            h = self._host.numpy()
+            for r, (p, i) in enumerate(zip(params, indices)):
+                h[0, r] = 0.0 if p.greedy else p.temperature
+                h[1, r] = uniform_draw(p.seed, i)
+            self._dev[:, :n].copy_(self._host[:, :n], non_blocking=True)
+            if any(p.has_filters and not p.greedy for p in params):
+                ops.filter_logits(logits, params)
+            ops.sample(logits, self._dev[0, :n], self._dev[1, :n], out)
+        self._out_host[:n].copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._out_host[:n].tolist()

@@ -1,0 +1,210 @@
+"""Generation through the Python entry point and the command line, compared with
+the plain implementation: greedy and temperature sampling, several requests at
+once equal to each alone, pages running out in flight, and the sampling kernels
+alone against the plain sampler."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import plain_llama as P
+from helpers import TINY, make_tiny, random_prompt
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def tiny(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("engine_models")
+    return {w: make_tiny(tmp, w, "bfloat16") for w in TINY}
+
+
+def _engine(model_dir, **kw):
+    import mlxforge_b200 as mf
+    opts = dict(model_spec=model_dir, dtype="float32", kv_pool_tokens=2048, max_running=8)
+    opts.update(kw)
+    return mf.Engine(**opts)
+
+
+@pytest.mark.parametrize("which,lengths,steps", [("A", [5, 17, 31], 8), ("B", [1, 9, 40, 70], 12)])
+def test_greedy_generation_matches_plain(tiny, which, lengths, steps):
+    d, cfg, w = tiny[which]
+    eng = _engine(d)
+    prompts = [random_prompt(cfg, n, 10 + i) for i, n in enumerate(lengths)]
+    expected = [P.generate(cfg, w, p, steps) for p in prompts]
+    # each alone
+    for p, e in zip(prompts, expected):
+        assert eng.generate(p, max_tokens=steps) == e
+    # all at once: the same tokens as alone (the reference's strongest property,
+    # tests/scheduler/validation_test.cpp:44-89)
+    assert eng.generate(prompts, max_tokens=steps) == expected
+    # and in portions of 7 beside decoding requests
+    eng2 = _engine(d, prefill_chunk=7, token_budget=16)
+    assert eng2.generate(prompts, max_tokens=steps) == expected
+    m = eng2.metrics()
+    assert m["completed"] == len(prompts) and m["pages_free"] == m["pages_total"]
+
+
+def test_bfloat16_greedy_agrees_where_the_margin_is_clear(tiny):
+    d, cfg, w = tiny["B"]
+    eng = _engine(d, dtype="bfloat16")
+    for i, n in enumerate([9, 40]):
+        p = random_prompt(cfg, n, 30 + i)
+        got = eng.generate(p, max_tokens=10)
+        seq = list(p)
+        for t in got:
+            row = P.forward_logits(cfg, w, seq)[-1]
+            top2 = np.sort(row)[-2:]
+            if top2[1] - top2[0] > 0.05:          # far beyond bfloat16 noise on these logits
+                assert t == int(np.argmax(row))
+            seq.append(t)
+
+
+def test_temperature_sampling_matches_plain(tiny):
+    import mlxforge_b200 as mf
+    d, cfg, w = tiny["B"]
+    eng = _engine(d)
+    prompt = random_prompt(cfg, 40, 77)
+    done = 0
+    for seed in range(20):
+        # the plain run, noting how close each draw came to an edge of the CDF
+        seq, exp, margin = list(prompt), [], 1.0
+        for i in range(12):
+            row = P.forward_logits(cfg, w, seq)[-1]
+            t, m = P.sample_token(row, 0.8, P.uniform_for(seed, i))
+            margin = min(margin, m)
+            exp.append(t)
+            seq.append(t)
+        if margin < 1e-5:
+            continue      # a draw on an edge decides by rounding; such seeds prove nothing
+        got = eng.generate(prompt, mf.SamplingParams(temperature=0.8, seed=seed), max_tokens=12)
+        assert got == exp, f"seed {seed}"
+        done += 1
+        if done == 3:
+            break
+    assert done == 3
+    assert len(set(exp)) > 3, "temperature sampling should not collapse to one token"
+
+
+def test_eos_stops_and_is_not_emitted(tiny):
+    d, cfg, w = tiny["A"]
+    eng = _engine(d)
+    p = random_prompt(cfg, 17, 5)
+    full = P.generate(cfg, w, p, 8)
+    req = eng.submit_ids(p, None, 8, eos_ids=[full[3]])
+    req.params = __import__("mlxforge_b200").GREEDY
+    eng.run_until_idle()
+    first = full.index(full[3])
+    assert req.output_ids == full[:first] and req.finish_reason == "stop"
+    assert list(req) == full[:first]
+
+
+def test_pages_run_out_in_flight(tiny):
+    """A pool too small for all requests at once: some are preempted and recomputed,
+    and every request still produces exactly its own tokens."""
+    d, cfg, w = tiny["A"]
+    prompts = [random_prompt(cfg, n, 50 + i) for i, n in enumerate([30, 25, 20, 28])]
+    expected = [P.generate(cfg, w, p, 20) for p in prompts]
+    eng = _engine(d, kv_pool_tokens=112, max_running=4)       # 7 pages of 16 for 4 x ~50 tokens
+    assert eng.generate(prompts, max_tokens=20) == expected
+    m = eng.metrics()
+    assert m["preemptions"] >= 1 and m["pages_free"] == m["pages_total"]
+    eng.cache.check()
+
+
+def test_worker_thread_and_cancel(tiny):
+    import mlxforge_b200 as mf
+    d, cfg, w = tiny["A"]
+    eng = _engine(d)
+    eng.start()
+    p = random_prompt(cfg, 12, 3)
+    a = eng.submit_ids(p, mf.GREEDY, 8)
+    b = eng.submit_ids(p, mf.GREEDY, 100000)
+    assert list(a) == P.generate(cfg, w, p, 8)
+    b.cancel()
+    while b.next(timeout=10) is not None:
+        pass
+    assert b.finish_reason == "cancel"
+    eng.stop()
+    assert eng.scheduler.idle
+
+
+def test_cli_generate_and_replay(tiny, tmp_path):
+    d, cfg, w = tiny["A"]
+    p = random_prompt(cfg, 9, 1)
+    np.save(tmp_path / "ids.npy", np.asarray(p, dtype=np.int32))
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    out = subprocess.run([sys.executable, "-m", "mlxforge_b200", "generate", d, str(tmp_path / "ids.npy"), "6",
+                          "--dtype", "float32"], capture_output=True, text=True, env=env, timeout=600)
+    assert out.returncode == 0, out.stderr
+    assert [int(t) for t in out.stdout.split()] == P.generate(cfg, w, p, 6)
+    assert "time to first token" in out.stderr
+    trace = '{"step": 0, "entries": [{"id": "a", "tokens": %s, "want": [8]}], "end": ["a"]}\n' % p
+    out = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", "float32", "--out",
+                          str(tmp_path / "o"), "--max-tokens", "64"], input=trace, capture_output=True,
+                         text=True, timeout=600)
+    assert out.returncode == 0 and out.stdout.strip() == "done 0", out.stderr
+    got = np.fromfile(tmp_path / "o" / "0.f32", dtype="<f4")
+    assert np.max(np.abs(got - P.forward_logits(cfg, w, p)[-1])) < 1e-4
+
+
+# ----------------------------------------------------------------------------- sampling kernels alone
+
+@pytest.mark.parametrize("V", [307, 4096, 128256])
+def test_sample_kernel_against_plain(V):
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(V)
+    n = 6
+    logits = (rng.standard_normal((n, V)) * 2.0).astype(np.float32)
+    logits[0, 5] = logits[0, 200] = logits[0].max() + 1.0          # a tie: lowest index wins
+    temps = np.array([0.0, 0.7, 1.0, 1.3, 0.0, 0.5], dtype=np.float32)
+    us = np.array([0.3, 0.123, 0.999, 0.5, 0.0, 0.0], dtype=np.float32)
+    dl = torch.from_numpy(logits).cuda()
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    ops.sample(dl, None, None, out)
+    assert out.tolist() == [int(np.argmax(r)) for r in logits] and out[0].item() == 5
+    ops.sample(dl, torch.from_numpy(temps).cuda(), torch.from_numpy(us).cuda(), out)
+    for r in range(n):
+        tok, margin = P.sample_token(logits[r], float(temps[r]), float(us[r]))
+        if margin > 1e-5:
+            assert out[r].item() == tok, (r, tok, out[r].item())
+
+
+def test_filters_and_penalties_against_plain():
+    import torch
+    import mlxforge_b200 as mf
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(9)
+    V = 5003
+    cases = [mf.SamplingParams(temperature=0.9, top_k=40), mf.SamplingParams(temperature=1.2, top_p=0.85),
+             mf.SamplingParams(temperature=0.6, min_p=0.05),
+             mf.SamplingParams(temperature=0.8, top_k=200, top_p=0.9, min_p=0.01),
+             mf.SamplingParams(temperature=0.0, top_k=5), mf.SamplingParams(temperature=1.0, top_k=V + 10)]
+    logits = (rng.standard_normal((len(cases), V)) * 3.0).astype(np.float32)
+    dl = torch.from_numpy(logits.copy()).cuda()
+    ops.filter_logits(dl, cases)
+    got = dl.cpu().numpy()
+    for r, p in enumerate(cases):
+        if p.greedy:
+            assert np.array_equal(got[r], logits[r])
+            continue
+        want = P.filter_logits(logits[r], p.temperature, p.top_k, p.top_p, p.min_p)
+        kept_want, kept_got = np.isfinite(want), np.isfinite(got[r])
+        # the two may differ only on entries whose probability sits on a threshold
+        diff = np.flatnonzero(kept_want != kept_got)
+        assert diff.size <= 1, (r, diff)
+        assert np.array_equal(got[r][kept_got], logits[r][kept_got])
+    hist = [list(rng.integers(0, V, size=50)) + [7, 7, 7], [], list(range(10))]
+    pp = [mf.SamplingParams(repetition_penalty=1.3, frequency_penalty=0.2, presence_penalty=0.4),
+          mf.SamplingParams(), mf.SamplingParams(repetition_penalty=0.8)]
+    logits = (rng.standard_normal((3, V)) * 3.0).astype(np.float32)
+    dl = torch.from_numpy(logits.copy()).cuda()
+    ops.apply_penalties(dl, pp, hist)
+    got = dl.cpu().numpy()
+    for r, p in enumerate(pp):
+        want = P.apply_penalties(logits[r], hist[r], p.repetition_penalty, p.frequency_penalty, p.presence_penalty)
+        assert np.max(np.abs(got[r] - want)) < 1e-5
