@@ -98,6 +98,7 @@ class Engine:
         self._thread: Optional[threading.Thread] = None
         self._stop = False
         self._t_busy = 0.0
+        self._device_index = rt.device.index if rt.device.index is not None else torch.cuda.current_device()
 
     # ------------------------------------------------------------------ submit
     @property
@@ -165,18 +166,25 @@ class Engine:
         self._thread.start()
 
     def _run(self) -> None:
-        torch.cuda.set_device(self.model.rt.device)
-        while True:
-            with self._wake:
-                while self.scheduler.idle and not self._stop:
-                    self._wake.wait(timeout=0.1)
-                if self._stop and self.scheduler.idle:
-                    return
-            try:
-                self.step()
-            except Exception:
-                if self._stop:
-                    return
+        try:
+            torch.cuda.set_device(self._device_index)
+            while True:
+                with self._wake:
+                    while self.scheduler.idle and not self._stop:
+                        self._wake.wait(timeout=0.1)
+                    if self._stop and self.scheduler.idle:
+                        return
+                try:
+                    self.step()
+                except Exception:
+                    # step() has already ended every request with "error"; the
+                    # worker itself stays up for later requests
+                    if self._stop:
+                        return
+        except BaseException as exc:      # the worker cannot go on: nobody may wait forever
+            with self._lock:
+                self.scheduler.fail_all(f"worker died: {type(exc).__name__}: {exc}")
+            raise
 
     def stop(self) -> None:
         """Complete what is in flight, then end the worker (src/runtime/worker.cpp:191-194,231-233)."""
