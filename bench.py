@@ -1,0 +1,304 @@
+#!/usr/bin/env python3
+"""Headline benchmark: decode tokens/s of the Llama-3.2-1B shape in bfloat16 on one
+B200 (batch 8 at the stated context length), with prefill of 2,048 tokens, decode
+at batch 1 and 64, the same metric end to end through the Python entry point, and
+roofline fractions.  Prints ONE JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+A "step" is one decode step of the whole batch (model forward over the paged
+cache plus on-device sampling).  Weights are random (seeded normal, std 0.02),
+token ids are seeded uniform: there is no network for checkpoints or datasets.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: the Llama-3.2-1B shape
+LLAMA_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 16, "hidden_size": 2048,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192,
+    "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": True,
+}
+CONTEXT = 8192
+BATCH = 8
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+REFERENCE_UNAVAILABLE = ("hvasconcelos/mlxforge builds only on Apple (CMakeLists.txt:14-16 errors elsewhere) and "
+                         "computes through Apple MLX/Metal, which this box does not have; it has no pip package")
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        try:
+            with open(p) as f:
+                j = json.load(f)
+            hbm = j.get("hbm_gbs")
+            tf = j.get("bf16_tflops_sustained") or j.get("bf16_tflops")
+            if hbm and tf:
+                return {"hbm_gbs": float(hbm), "bf16_tflops": float(tf), "source": "measured"}
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi sampling SM clocks and throttle reasons while a region is timed."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.proc = None
+
+    def start(self):
+        exe = shutil.which("nvidia-smi")
+        if not exe:
+            return
+        self.f = open(self.path, "w")
+        self.proc = subprocess.Popen([exe, "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                      "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    c = [x.strip() for x in line.split(",")]
+                    if len(c) < 7:
+                        continue
+                    try:
+                        sm.append(float(c[0]))
+                        mx.append(float(c[1]))
+                    except ValueError:
+                        continue
+                    for n, v in zip(names, c[3:7]):
+                        if v.lower().startswith("active"):
+                            reasons.add(n)
+            os.remove(self.path)
+        except OSError:
+            pass
+        if sm:
+            out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
+        return out
+
+
+def decode_device(engine, batch, ctx, steps, warmup, seed=0):
+    """Device-timed decode: `batch` sequences whose cache holds ~ctx tokens (filled
+    with random keys and values, no forward pass needed for that), `warmup` + `steps`
+    decode steps of the step function with greedy sampling on the device.  Returns
+    (seconds per step, kernel launches per step, cache tokens read per step)."""
+    import numpy as np
+    import torch
+    from mlxforge_b200.csrc import binding, ops
+    from mlxforge_b200.engine.step import StepEntry
+    runner, cache = engine.runner, engine.cache
+    rng = np.random.default_rng(seed)
+    vocab = engine.model.spec.vocab_size
+    start_len = ctx - (warmup + steps)
+    seqs = [cache.open_sequence() for _ in range(batch)]
+    for s in seqs:
+        cache.reserve([(s, start_len)])
+        cache.commit(s, start_len)
+    out = torch.empty(batch, dtype=torch.int32, device="cuda")
+    toks = rng.integers(0, vocab, size=(warmup + steps, batch))
+
+    def one(i):
+        logits = runner.step([StepEntry(s, [int(toks[i, b])], [0]) for b, s in enumerate(seqs)])
+        ops.sample(logits, None, None, out)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    l0 = binding.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) / 1e3 / steps
+    launches = (binding.launch_count() - l0) / steps
+    mean_ctx = start_len + warmup + (steps + 1) / 2.0
+    for s in seqs:
+        cache.close(s)
+    return sec, launches, mean_ctx * batch
+
+
+def prefill_device(engine, tokens, runs=5, warmup=3):
+    import numpy as np
+    import torch
+    from mlxforge_b200.engine.step import StepEntry
+    runner, cache = engine.runner, engine.cache
+    rng = np.random.default_rng(1)
+    ids = rng.integers(0, engine.model.spec.vocab_size, size=tokens).tolist()
+    times = []
+    for i in range(warmup + runs):
+        s = cache.open_sequence()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.step([StepEntry(s, ids, [tokens - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        cache.close(s)
+        if i >= warmup:
+            times.append(e0.elapsed_time(e1) / 1e3)
+    return statistics.median(times)
+
+
+def decode_e2e(engine, batch, ctx, steps, warmup):
+    """The same metric through the Python entry point: requests with host token ids
+    in, generated ids out; every step copies its inputs from pinned host memory and
+    reads the sampled ids back."""
+    import numpy as np
+    import torch
+    import mlxforge_b200 as mf
+    rng = np.random.default_rng(2)
+    vocab = engine.model.spec.vocab_size
+    plen = ctx - (warmup + steps) - 1
+    reqs = [engine.submit_ids(rng.integers(0, vocab, size=plen).tolist(), mf.GREEDY, warmup + steps + 1, eos_ids=[])
+            for _ in range(batch)]
+    while any(len(r.output_ids) < 1 for r in reqs):          # prefill and first token, untimed
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    n0 = sum(len(r.output_ids) for r in reqs)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    n1 = sum(len(r.output_ids) for r in reqs)
+    h2d = engine.runner.last_meta_bytes
+    engine.run_until_idle()
+    return (n1 - n0) / (t1 - t0), h2d, batch * 4
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=LLAMA_1B["num_hidden_layers"])
+    ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--skip-points", action="store_true", help="only the headline batch")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"unavailable": f"this engine runs on one GPU; --gpus {args.gpus} is not supported"}))
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import mlxforge_b200 as mf
+    from mlxforge_b200.config import config_from_json
+
+    cfg_json = dict(LLAMA_1B, num_hidden_layers=args.layers)
+    tmp = tempfile.mkdtemp(prefix="mlxforge_bench_")
+    try:
+        t0 = time.time()
+        model_dir = mf.write_random_model(os.path.join(tmp, "llama_1b_random"), config_from_json(cfg_json), seed=0,
+                                          dtype="bfloat16")
+        ctx = args.context
+        engine = mf.Engine(model_spec=model_dir, dtype="bfloat16", kv_pool_tokens=64 * (ctx + 64), max_running=64,
+                           token_budget=8192, prefill_chunk=2048)
+        print(f"[bench] model written and loaded in {time.time() - t0:.0f}s", file=sys.stderr, flush=True)
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    # the synthetic cache: random keys and values everywhere (reading zeros is as slow, but keep it honest)
+    for pool in engine.cache._k + engine.cache._v:
+        pool.normal_(0.0, 1.0)
+
+    pk = peaks()
+    weight_bytes = engine.model.weight_bytes()
+    kv_per_token = engine.model.cache_layout.bytes_per_token(2)
+
+    clocks = ClockSampler()
+    clocks.start()
+    sec, launches, kv_tokens = decode_device(engine, BATCH, ctx, args.steps, args.warmup)
+    clk = clocks.stop()
+    value = BATCH / sec
+    bytes_step = weight_bytes + kv_tokens * kv_per_token
+    achieved = bytes_step / sec / 1e9
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            s_b, _, _ = decode_device(engine, b, ctx, max(8, args.steps // 2), args.warmup, seed=b)
+            points[f"decode_b{b}"] = round(b / s_b, 1)
+
+    t_pre = prefill_device(engine, PREFILL_TOKENS)
+    c = cfg_json
+    L, H, I, V = c["num_hidden_layers"], c["hidden_size"], c["intermediate_size"], c["vocab_size"]
+    nh, nkv, hd = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+    mat = L * (H * (nh + 2 * nkv) * hd + nh * hd * H + 3 * H * I)
+    T = PREFILL_TOKENS
+    flops = 2.0 * T * mat + 2.0 * V * H + L * 2.0 * T * T * hd * nh     # products + one head row + causal attention
+    prefill = {"value": round(T / t_pre, 1), "tokens": T, "ms": round(t_pre * 1e3, 3),
+               "frac": round(flops / t_pre / (pk["bf16_tflops"] * 1e12), 4)}
+
+    e2e_value, h2d, d2h = decode_e2e(engine, BATCH, ctx, args.steps, args.warmup)
+
+    line = {
+        "metric": "decode tok/s @ batch 8 (Llama-3.2-1B bf16)", "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded normal(0, 0.02) weights, seeded uniform token ids, random cache contents",
+        "config": {
+            "model": "Llama-3.2-1B shape (LlamaForCausalLM)", "layers": L, "layers_of_named_config": 16,
+            "hidden": H, "heads": nh, "kv_heads": nkv, "head_dim": hd, "intermediate": I, "vocab": V,
+            "global_batch": BATCH, "seq_len": ctx, "context_len": ctx, "kv_block": engine.cache.page_size,
+            "prefill_tokens": T, "parallelism": "single GPU",
+            "l2": "working set per step (weights + live cache) exceeds L2 many times; no flush needed",
+            "peaks": pk["source"],
+        },
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": int(round(launches * args.steps)),
+        "clocks": clk,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -65,8 +65,24 @@ def declare(name: str, argtypes) -> None:
         fn.restype = c_int
 
 
-def check(code: int, what: str) -> None:
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Kernel launches of this library so far in this process (every entry point
+    reports how many kernels it launched; graph replays add their kernel nodes)."""
+    return _LAUNCHES
+
+
+def count_launches(n: int) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
+def check(code: int, what: str, launches: int = 1) -> None:
     if code == 0:
+        global _LAUNCHES
+        _LAUNCHES += launches
         return
     if code in MF_ERRORS:
         raise KernelError(f"{what}: refused: {MF_ERRORS[code]}")

@@ -84,6 +84,7 @@ class ModelRunner:
         self._meta: Optional[torch.Tensor] = None
         self._copied = torch.cuda.Event()
         self._copy_pending = False
+        self.last_meta_bytes = 0
         self.steps = 0
 
     # ------------------------------------------------------------------ the step
@@ -174,6 +175,7 @@ class ModelRunner:
         host = self._pinned.numpy()
         for p, off in zip(parts, offsets):
             host[off:off + p.size] = p
+        self.last_meta_bytes = total * 4
         self._meta[:total].copy_(self._pinned[:total], non_blocking=True)
         self._copied.record()
         self._copy_pending = True

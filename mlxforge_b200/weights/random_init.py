@@ -18,7 +18,7 @@ import numpy as np
 
 from ..config.model_config import ModelConfig
 from ..config.registry import get_architecture
-from .safetensors_io import write_safetensors
+from .safetensors_io import write_safetensors_streaming
 
 
 def float32_to_bfloat16_bits(a: np.ndarray) -> np.ndarray:
@@ -33,29 +33,35 @@ def write_random_model(model_dir: str, config: ModelConfig, seed: int, *, dtype:
     """Write ``model_dir/config.json`` and ``model_dir/model.safetensors``.
 
     ``dtype`` is the storage type of every tensor: ``"bfloat16"`` or ``"float32"``.
-    Returns ``model_dir``.
+    Tensors are generated and written one at a time (torch's CPU generator, one
+    stream per tensor seeded by ``(seed, position in the file)``).  Returns
+    ``model_dir``.
     """
+    import torch
     if dtype not in ("bfloat16", "float32"):
         raise ValueError(f"random weights: dtype must be 'bfloat16' or 'float32', got '{dtype}'")
     arch = get_architecture(config.architecture)
     if arch.random_tensors is None:
         raise ValueError(f"architecture '{config.architecture}' does not describe its tensors for random weights")
     os.makedirs(model_dir, exist_ok=True)
-    items = []
-    for index, (name, shape, kind) in enumerate(arch.random_tensors(config)):
-        rng = np.random.Generator(np.random.Philox(key=[int(seed) & (2**64 - 1), index]))
+    tensors = list(arch.random_tensors(config))
+    tag = "BF16" if dtype == "bfloat16" else "F32"
+
+    def produce(i):
+        name, shape, kind = tensors[i]
+        g = torch.Generator().manual_seed((int(seed) * 1000003 + i) & (2**63 - 1))
         if kind == "norm":
-            a = np.ones(shape, dtype=np.float32)
+            a = torch.ones(shape, dtype=torch.float32)
             if norm_std:
-                a += rng.standard_normal(shape, dtype=np.float32) * np.float32(norm_std)
+                a += torch.empty(shape, dtype=torch.float32).normal_(0.0, float(norm_std), generator=g)
         else:
-            a = rng.standard_normal(shape, dtype=np.float32)
-            a *= np.float32(std)
+            a = torch.empty(shape, dtype=torch.float32).normal_(0.0, float(std), generator=g)
         if dtype == "bfloat16":
-            items.append((name, "BF16", tuple(shape), float32_to_bfloat16_bits(a).tobytes()))
-        else:
-            items.append((name, "F32", tuple(shape), a.tobytes()))
-    write_safetensors(os.path.join(model_dir, "model.safetensors"), items)
+            return a.to(torch.bfloat16).view(torch.int16).numpy()
+        return a.numpy()
+
+    write_safetensors_streaming(os.path.join(model_dir, "model.safetensors"),
+                                [(n, tag, tuple(s)) for n, s, _ in tensors], produce)
     j = config.to_json()
     j["torch_dtype"] = dtype
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:

@@ -154,3 +154,35 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, str, Tuple[int, ..
         for _, _, _, data in items:
             f.write(data)
     os.replace(tmp, path)
+
+
+def write_safetensors_streaming(path: str, entries, produce) -> None:
+    """Write a file whose tensors are made one at a time: ``entries`` is a list of
+    ``(name, dtype tag, shape)`` and ``produce(i)`` returns the raw little-endian
+    bytes (any buffer) of entry ``i``.  The header is computed from the shapes, so
+    a multi-gigabyte model never sits in memory."""
+    header: Dict[str, dict] = {}
+    off = 0
+    sizes = []
+    for name, dtype, shape in entries:
+        if dtype not in _DTYPES:
+            raise SafetensorsError(f"safetensors: cannot write dtype '{dtype}'")
+        n = _DTYPES[dtype][1]
+        for s_ in shape:
+            n *= int(s_)
+        header[name] = {"dtype": dtype, "shape": list(shape), "data_offsets": [off, off + n]}
+        sizes.append(n)
+        off += n
+    header["__metadata__"] = {"format": "pt"}
+    blob = json.dumps(header, separators=(",", ":")).encode("utf-8")
+    blob += b" " * ((8 - len(blob) % 8) % 8)
+    tmp = path + ".tmp"
+    with open(tmp, "wb") as f:
+        f.write(struct.pack("<Q", len(blob)))
+        f.write(blob)
+        for i, n in enumerate(sizes):
+            data = memoryview(produce(i)).cast("B")
+            if data.nbytes != n:
+                raise SafetensorsError(f"safetensors: tensor {entries[i][0]} produced {data.nbytes} bytes, expected {n}")
+            f.write(data)
+    os.replace(tmp, path)
