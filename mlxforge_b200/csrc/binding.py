@@ -27,6 +27,9 @@ _SIGNATURES = {
     "mf_attention_generic": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,
                              c_float, c_int, _P],
     "mf_sample": [_P, c_int, c_int, c_longlong, _P, _P, _P, _P],
+    "mf_attention_decode_split": [c_int],
+    "mf_attention_decode": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,
+                            c_float, c_int, c_int, _P],
     "mf_apply_penalties": [_P, c_int, c_longlong, _P, _P, _P, _P, _P, _P, _P],
     "mf_filter_logits": [_P, c_int, c_int, c_longlong, _P, _P, _P, _P, _P],
 }

@@ -197,7 +197,20 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ attention dispatch
     def attention(self, batch: StepBatch, q, lane: KVLane, out, n_heads: int, scale: float, window: int) -> None:
+        """bfloat16: the sequences that bring one token (they come first in the
+        batch) go to the split-key decode kernel, the others to the prefill
+        kernel.  float32: the generic kernel for all."""
         need = lane.need
-        ops.attention_generic(q, lane.k, lane.v, out, batch.positions, batch.seq_of_token,
-                              batch.block_table(lane.group), lane.page_size, n_heads, need.n_kv_heads,
-                              need.head_dim, scale, window)
+        table = batch.block_table(lane.group)
+        nd = batch.n_decode if q.dtype == torch.bfloat16 else 0
+        if nd > 0:
+            n_o, n_ml = ops.attention_decode_scratch(nd, n_heads, need.head_dim, batch.max_ctx)
+            ops.attention_decode(q[:nd], lane.k, lane.v, out[:nd],
+                                 self.rt.buffer("attn.part_o", (n_o,), torch.float32),
+                                 self.rt.buffer("attn.part_ml", (n_ml,), torch.float32),
+                                 batch.positions[:nd], batch.seq_of_token[:nd], table, lane.page_size, n_heads,
+                                 need.n_kv_heads, need.head_dim, scale, window, batch.max_ctx)
+        if nd < batch.n_tokens:
+            ops.attention_generic(q[nd:], lane.k, lane.v, out[nd:], batch.positions[nd:],
+                                  batch.seq_of_token[nd:], table, lane.page_size, n_heads, need.n_kv_heads,
+                                  need.head_dim, scale, window)

@@ -1,0 +1,303 @@
+"""Each CUDA kernel alone against a plain NumPy reference of the same operation,
+at sizes other than the engine's test models: head sizes in steps of 16, widths
+and vocabularies that are no power of two, odd numbers of heads and groups,
+pages in scrambled order, windows, and inputs built so that one far key or one
+page's edge decides the result."""
+import numpy as np
+import pytest
+
+import plain_llama as P
+from helpers import bf16_round
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a, dtype=None):
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def host(t):
+    import torch
+    return t.detach().to("cpu", torch.float32).numpy().astype(np.float64)
+
+
+def torch_dtype(name):
+    import torch
+    return {"float32": torch.float32, "bfloat16": torch.bfloat16}[name]
+
+
+# ----------------------------------------------------------------------------- embedding, norm, swiglu
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("V,H,T", [(307, 80, 5), (1000, 2048, 33), (50, 24, 1)])
+def test_embed(dtype, V, H, T):
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(0)
+    table = bf16_round(rng.standard_normal((V, H)).astype(np.float32))
+    toks = rng.integers(0, V, size=T).astype(np.int32)
+    toks[0] = V - 1
+    out = torch.empty((T, H), dtype=torch.float32, device="cuda")
+    ops.embed(dev(table, torch_dtype(dtype)), dev(toks), out)
+    assert np.array_equal(host(out), P.embed(table.astype(np.float64), toks))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,T,eps", [(80, 7, 1e-5), (2048, 3, 1e-6), (1000, 5, 3e-5), (24, 1, 1e-5)])
+def test_add_rmsnorm(dtype, H, T, eps):
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(1)
+    td = torch_dtype(dtype)
+    resid = rng.standard_normal((T, H)).astype(np.float32) * 3.0
+    delta = bf16_round(rng.standard_normal((T, H)).astype(np.float32))
+    w = (1.0 + 0.3 * rng.standard_normal(H)).astype(np.float32)
+    tol = 1e-5 if dtype == "float32" else 2.0 ** -7
+    # plain norm
+    r = dev(resid)
+    out = torch.empty((T, H), dtype=td, device="cuda")
+    ops.add_rmsnorm(r, None, dev(w), eps, out)
+    want = P.rms_norm(resid.astype(np.float64), w.astype(np.float64), eps)
+    assert np.max(np.abs(host(out) - want) / (np.abs(want) + 1.0)) < tol
+    assert np.array_equal(host(r), resid)
+    # add + norm: the residual moves on, in 32-bit
+    ops.add_rmsnorm(r, dev(delta, td), dev(w), eps, out)
+    summed = resid.astype(np.float64) + delta
+    assert np.max(np.abs(host(r) - summed)) < 1e-6
+    want = P.rms_norm(summed, w.astype(np.float64), eps)
+    assert np.max(np.abs(host(out) - want) / (np.abs(want) + 1.0)) < tol
+    # selected rows: nothing is written back
+    r2 = dev(resid)
+    rows = np.array([T - 1, 0], dtype=np.int32)
+    out2 = torch.empty((2, H), dtype=td, device="cuda")
+    ops.add_rmsnorm(r2, dev(delta, td), dev(w), eps, out2, dev(rows))
+    assert np.array_equal(host(r2), resid)
+    assert np.max(np.abs(host(out2) - want[rows]) / (np.abs(want[rows]) + 1.0)) < tol
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("I,T,group", [(136, 5, 8), (100, 3, 100), (8192, 2, 8)])
+def test_swiglu(dtype, I, T, group):
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(2)
+    g = bf16_round(rng.standard_normal((T, I)).astype(np.float32) * 2)
+    u = bf16_round(rng.standard_normal((T, I)).astype(np.float32))
+    n = I // group
+    gu = np.stack([g.reshape(T, n, group), u.reshape(T, n, group)], axis=2).reshape(T, 2 * I)
+    out = torch.empty((T, I), dtype=torch_dtype(dtype), device="cuda")
+    ops.swiglu(dev(gu, torch_dtype(dtype)), out, group)
+    want = g.astype(np.float64) / (1 + np.exp(-g.astype(np.float64))) * u
+    assert np.max(np.abs(host(out) - want)) < (1e-6 if dtype == "float32" else 2.0 ** -7 * np.abs(want).max())
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 307, 80), (33, 96, 200), (70, 1000, 17), (128, 64, 64)])
+def test_gemm_f32_is_ieee(M, N, K):
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = rng.standard_normal((N, K)).astype(np.float32)
+    out = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    ops.gemm_f32(dev(a), dev(w), out)
+    want = a.astype(np.float64) @ w.astype(np.float64).T
+    # a reduced-precision product mode would be off by ~1e-3 relative; IEEE float32 by ~1e-6
+    assert np.max(np.abs(host(out) - want)) < 2e-5 * np.sqrt(K)
+    # rows do not depend on how many other rows there are
+    out1 = torch.empty((1, N), dtype=torch.float32, device="cuda")
+    ops.gemm_f32(dev(a[M // 2:M // 2 + 1]), dev(w), out1)
+    assert torch.equal(out1[0], out[M // 2])
+
+
+# ----------------------------------------------------------------------------- paged cache helpers
+
+class Paged:
+    """Sequences with keys and values laid out in scrambled pages, and the same
+    data as plain per-sequence arrays for the reference."""
+
+    def __init__(self, lengths, nkv, hd, page=16, dtype="float32", seed=0, extra_pages=7):
+        import torch
+        rng = np.random.default_rng(seed)
+        self.page, self.nkv, self.hd = page, nkv, hd
+        blocks = [(n + page - 1) // page for n in lengths]
+        n_pages = sum(blocks) + extra_pages
+        perm = rng.permutation(n_pages)
+        self.k = [bf16_round(rng.standard_normal((n, nkv, hd)).astype(np.float32)) for n in lengths]
+        self.v = [bf16_round(rng.standard_normal((n, nkv, hd)).astype(np.float32)) for n in lengths]
+        # unused pages and the tails of last pages hold NaN: reading them shows
+        kp = np.full((n_pages, nkv, page, hd), np.nan, dtype=np.float32)
+        vp = np.full((n_pages, nkv, page, hd), np.nan, dtype=np.float32)
+        self.table = np.full((len(lengths), max(blocks)), -1, dtype=np.int32)
+        at = 0
+        for s, n in enumerate(lengths):
+            for b in range(blocks[s]):
+                pg = perm[at]
+                at += 1
+                self.table[s, b] = pg
+                m = min(page, n - b * page)
+                kp[pg, :, :m] = self.k[s][b * page:b * page + m].transpose(1, 0, 2)
+                vp[pg, :, :m] = self.v[s][b * page:b * page + m].transpose(1, 0, 2)
+        td = torch_dtype(dtype)
+        self.k_pool, self.v_pool = dev(kp, td), dev(vp, td)
+        self.table_dev = dev(self.table)
+
+    def reference(self, q, seq, pos, scale, window=0):
+        """q [nh, hd] -> [nh, hd] over keys [lo, pos] of sequence seq."""
+        nh = q.shape[0]
+        rep = nh // self.nkv
+        lo = max(0, pos - window + 1) if window > 0 else 0
+        out = np.empty_like(q, dtype=np.float64)
+        for h in range(nh):
+            k = self.k[seq][lo:pos + 1, h // rep].astype(np.float64)
+            v = self.v[seq][lo:pos + 1, h // rep].astype(np.float64)
+            s = (k @ q[h].astype(np.float64)) * scale
+            p = np.exp(s - s.max())
+            out[h] = (p / p.sum()) @ v
+        return out
+
+
+ATTN_CASES = [
+    # nh, nkv, hd, lengths, window
+    (4, 2, 16, [1, 17, 40], 0),
+    (6, 1, 32, [300, 5, 129], 0),
+    (5, 5, 48, [64, 65, 200], 0),
+    (32, 8, 64, [1000, 257], 0),
+    (8, 2, 128, [130, 31], 0),
+    (3, 1, 256, [70], 0),
+    (40, 2, 64, [90, 33], 0),          # 20 query heads per KV head: two groups of 16
+    (4, 2, 32, [300, 40, 129], 37),    # a window
+]
+
+
+@pytest.mark.parametrize("case", ATTN_CASES)
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_generic(case, dtype):
+    import torch
+    from mlxforge_b200.csrc import ops
+    nh, nkv, hd, lengths, window = case
+    pc = Paged(lengths, nkv, hd, dtype=dtype, seed=hd)
+    rng = np.random.default_rng(5)
+    # queries: the last token of every sequence, plus a run of tokens in the middle of the first
+    toks = [(s, n - 1) for s, n in enumerate(lengths)] + [(0, p) for p in range(max(0, lengths[0] - 5), lengths[0] - 1)]
+    q = bf16_round(rng.standard_normal((len(toks), nh, hd)).astype(np.float32))
+    out = torch.empty((len(toks), nh * hd), dtype=torch_dtype(dtype), device="cuda")
+    scale = hd ** -0.5
+    ops.attention_generic(dev(q.reshape(len(toks), -1), torch_dtype(dtype)), pc.k_pool, pc.v_pool, out,
+                          dev(np.array([p for _, p in toks], dtype=np.int32)),
+                          dev(np.array([s for s, _ in toks], dtype=np.int32)), pc.table_dev, pc.page, nh, nkv, hd,
+                          scale, window)
+    got = host(out).reshape(len(toks), nh, hd)
+    tol = 2e-5 if dtype == "float32" else 1.5e-2
+    for i, (s, p) in enumerate(toks):
+        want = pc.reference(q[i], s, p, scale, window)
+        assert np.max(np.abs(got[i] - want)) < tol, (i, s, p)
+
+
+@pytest.mark.parametrize("case", ATTN_CASES)
+def test_attention_decode(case):
+    import torch
+    from mlxforge_b200.csrc import ops
+    nh, nkv, hd, lengths, window = case
+    pc = Paged(lengths, nkv, hd, dtype="bfloat16", seed=hd + 1)
+    rng = np.random.default_rng(6)
+    n = len(lengths)
+    q = bf16_round(rng.standard_normal((n, nh, hd)).astype(np.float32))
+    scale = hd ** -0.5
+    pos = np.array([m - 1 for m in lengths], dtype=np.int32)
+    max_ctx = max(lengths) + 3
+    n_o, n_ml = ops.attention_decode_scratch(n, nh, hd, max_ctx)
+    out = torch.full((n, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.attention_decode(dev(q.reshape(n, -1), torch.bfloat16), pc.k_pool, pc.v_pool, out,
+                         torch.full((n_o,), float("nan"), dtype=torch.float32, device="cuda"),
+                         torch.full((n_ml,), float("nan"), dtype=torch.float32, device="cuda"),
+                         dev(pos), dev(np.arange(n, dtype=np.int32)), pc.table_dev, pc.page, nh, nkv, hd, scale,
+                         window, max_ctx)
+    got = host(out).reshape(n, nh, hd)
+    for s in range(n):
+        want = pc.reference(q[s], s, int(pos[s]), scale, window)
+        assert np.max(np.abs(got[s] - want)) < 1.5e-2, (s, np.max(np.abs(got[s] - want)))
+
+
+@pytest.mark.parametrize("kernel", ["generic32", "generic16", "decode"])
+def test_one_far_key_decides(kernel):
+    """Among a thousand keys one, far back and at the first slot of a page, matches
+    the query: the output must be that key's value.  A kernel that drops a key, a
+    page or a split shows here, where random scores would hide it."""
+    import torch
+    from mlxforge_b200.csrc import ops
+    nh, nkv, hd, n = 8, 2, 64, 1000
+    dtype = "float32" if kernel == "generic32" else "bfloat16"
+    for special in (0, 16, 255, 256, 511, 640, 999):
+        pc = Paged([n], nkv, hd, dtype="float32", seed=special)
+        q = np.zeros((1, nh, hd), dtype=np.float32)
+        for h in range(nh):
+            pc.k[0][:, h // 4] *= 0.05
+            q[0, h] = 1.0
+        pc.k[0][special, :, :] = 4.0            # score 4 * 64 / 8 = 32 against ~0 for the rest
+        pc2 = Paged.__new__(Paged)
+        # rebuild the pools from the edited arrays
+        pc2.__dict__.update(pc.__dict__)
+        kp = np.full(tuple(pc.k_pool.shape), np.nan, dtype=np.float32)
+        for b in range(pc.table.shape[1]):
+            m = min(16, n - b * 16)
+            kp[pc.table[0, b], :, :m] = pc.k[0][b * 16:b * 16 + m].transpose(1, 0, 2)
+        td = torch_dtype(dtype)
+        k_pool, v_pool = dev(kp, td), pc.v_pool.to(td)
+        out = torch.empty((1, nh * hd), dtype=td, device="cuda")
+        args = (dev(np.array([n - 1], dtype=np.int32)), dev(np.array([0], dtype=np.int32)), pc.table_dev, 16, nh,
+                nkv, hd, hd ** -0.5, 0)
+        if kernel == "decode":
+            n_o, n_ml = ops.attention_decode_scratch(1, nh, hd, n)
+            ops.attention_decode(dev(q.reshape(1, -1), td), k_pool, v_pool, out,
+                                 torch.empty(n_o, dtype=torch.float32, device="cuda"),
+                                 torch.empty(n_ml, dtype=torch.float32, device="cuda"), *args, n)
+        else:
+            ops.attention_generic(dev(q.reshape(1, -1), td), k_pool, v_pool, out, *args)
+        got = host(out).reshape(nh, hd)
+        for h in range(nh):
+            assert np.max(np.abs(got[h] - pc.v[0][special, h // 4])) < 2e-2, (special, h)
+
+
+# ----------------------------------------------------------------------------- rope + cache write
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (6, 1, 32, 32), (5, 5, 48, 48), (3, 1, 64, 32), (2, 2, 32, 0)])
+def test_rope_kv_write(dtype, nh, nkv, hd, rot):
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(7)
+    td = torch_dtype(dtype)
+    page, n_pages = 16, 12
+    # two sequences: tokens 30..36 of the first (crossing a page edge at 32), token 5 of the second
+    seqs = np.array([0] * 7 + [1], dtype=np.int32)
+    poss = np.array(list(range(30, 37)) + [5], dtype=np.int32)
+    table = np.array([[7, 2, 9], [4, -1, -1]], dtype=np.int32)
+    T = len(seqs)
+    qkv = bf16_round(rng.standard_normal((T, (nh + 2 * nkv) * hd)).astype(np.float32))
+    freqs = np.power(np.float32(10000.0), np.arange(0, max(rot, 2), 2, dtype=np.float32) / np.float32(max(rot, 2)))
+    k_pool = torch.zeros((n_pages, nkv, page, hd), dtype=td, device="cuda")
+    v_pool = torch.zeros_like(k_pool)
+    q_out = torch.empty((T, nh * hd), dtype=td, device="cuda")
+    ops.rope_kv_write(dev(qkv, td), dev(poss), dev(seqs), dev(table), page, dev(freqs) if rot else None, q_out,
+                      k_pool, v_pool, nh, nkv, hd, rot, True, dtype == "float32")
+    x = qkv.astype(np.float64).reshape(T, nh + 2 * nkv, hd)
+
+    def rotate(heads):   # [T, h, hd]
+        if rot == 0:
+            return heads
+        r = P.apply_rope(heads[..., :rot].transpose(1, 0, 2), poss, freqs).transpose(1, 0, 2)
+        return np.concatenate([r, heads[..., rot:]], axis=-1)
+
+    tol = 1e-5 if dtype == "float32" else 2.0 ** -6
+    assert np.max(np.abs(host(q_out).reshape(T, nh, hd) - rotate(x[:, :nh]))) < tol * 4
+    want_k, want_v = rotate(x[:, nh:nh + nkv]), x[:, nh + nkv:]
+    kp, vp = host(k_pool), host(v_pool)
+    written = np.zeros((n_pages, page), dtype=bool)
+    for t in range(T):
+        pg, slot = table[seqs[t], poss[t] // page], poss[t] % page
+        written[pg, slot] = True
+        assert np.max(np.abs(kp[pg, :, slot] - want_k[t])) < tol * 4
+        assert np.max(np.abs(vp[pg, :, slot] - want_v[t])) < 1e-6
+    assert np.all(kp[~written] == 0) and np.all(vp[~written] == 0), "nothing else in the pools was touched"
