@@ -90,7 +90,9 @@ def test_swiglu(dtype, I, T, group):
     out = torch.empty((T, I), dtype=torch_dtype(dtype), device="cuda")
     ops.swiglu(dev(gu, torch_dtype(dtype)), out, group)
     want = g.astype(np.float64) / (1 + np.exp(-g.astype(np.float64))) * u
-    assert np.max(np.abs(host(out) - want)) < (1e-6 if dtype == "float32" else 2.0 ** -7 * np.abs(want).max())
+    # relative to each value: a few float32 (2^-24) or one bfloat16 (2^-8) roundings
+    rel = 2.0 ** -21 if dtype == "float32" else 2.0 ** -7
+    assert np.all(np.abs(host(out) - want) <= rel * (np.abs(want) + 1e-3))
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 307, 80), (33, 96, 200), (70, 1000, 17), (128, 64, 64)])
@@ -300,4 +302,6 @@ def test_rope_kv_write(dtype, nh, nkv, hd, rot):
         written[pg, slot] = True
         assert np.max(np.abs(kp[pg, :, slot] - want_k[t])) < tol * 4
         assert np.max(np.abs(vp[pg, :, slot] - want_v[t])) < 1e-6
-    assert np.all(kp[~written] == 0) and np.all(vp[~written] == 0), "nothing else in the pools was touched"
+    untouched = ~written                      # pools are [page][kv head][slot][channel]
+    assert np.all(kp.transpose(0, 2, 1, 3)[untouched] == 0) and np.all(vp.transpose(0, 2, 1, 3)[untouched] == 0), \
+        "nothing else in the pools was touched"
