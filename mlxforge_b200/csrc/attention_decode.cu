@@ -309,3 +309,84 @@ MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_
   return launch_decode<256>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token, scale,
                             window, max_ctx, stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// mf_attention_decode_static: the same attention, for callers that cannot give it scratch memory.
+// Declared and described in attention_decode_static.h.
+#include "attention_decode_static.h"
+
+#include <cstdio>
+#include <mutex>
+
+namespace {
+
+// The partial results of kernel 1 live here instead of in caller-provided buffers.  One copy per
+// GPU that loads this library, held until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[MF_DECODE_STATIC_SCRATCH_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_mutex;
+float* g_static_ptr[MAX_DEVICES] = {};     // device address of g_static_scratch, per device ordinal
+
+void say(char* err, int err_len, const char* fmt, long long a = 0, long long b = 0) {
+  if (err && err_len > 0) snprintf(err, (size_t)err_len, fmt, a, b);
+}
+
+}  // namespace
+
+MF_API long long mf_attention_decode_static_bytes(int n_tokens, int n_heads, int hd, int max_ctx) {
+  if (n_tokens <= 0 || n_heads <= 0 || hd <= 0 || max_ctx <= 0) return 0;
+  const int split = mf_attention_decode_split(hd);
+  const long long splits = (max_ctx + split - 1) / split;
+  return (long long)n_tokens * n_heads * splits * (hd + 2) * (long long)sizeof(float);
+}
+
+MF_API int mf_attention_decode_static(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                      int n_tokens, int n_heads, int n_kv, int hd, const int* positions,
+                                      const int* seq_of_token, const int* block_table, int bt_stride,
+                                      int page_size, float scale, int window, int max_ctx, cudaStream_t stream,
+                                      char* err, int err_len) {
+  if (n_tokens <= 0) return 0;
+  if (hd < 16 || hd > 256 || hd % 16 || n_kv <= 0 || n_heads <= 0 || n_heads % n_kv || max_ctx <= 0 ||
+      n_tokens > 65535) {
+    say(err, err_len, "mf_attention_decode_static: unsupported sizes (head size must be a multiple of 16 in "
+                      "[16, 256], heads a multiple of KV heads, at most 65535 tokens)");
+    return MF_ERR_BAD_ARG;
+  }
+  const long long need = mf_attention_decode_static_bytes(n_tokens, n_heads, hd, max_ctx);
+  if (need > (long long)MF_DECODE_STATIC_SCRATCH_BYTES) {
+    say(err, err_len, "mf_attention_decode_static: this call needs %lld bytes of scratch, the built-in array "
+                      "holds %lld; use mf_attention_decode with buffers of your own",
+        need, (long long)MF_DECODE_STATIC_SCRATCH_BYTES);
+    return MF_ERR_SCRATCH_LIMIT;
+  }
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= MAX_DEVICES) {
+    say(err, err_len, "mf_attention_decode_static: device ordinal %lld is beyond the %lld this table holds",
+        device, MAX_DEVICES);
+    return MF_ERR_BAD_ARG;
+  }
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_ptr[device] == nullptr) {
+      // In host code `g_static_scratch` is only a handle: the address the kernels may use is this one.
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess) {
+        say(err, err_len, "mf_attention_decode_static: cudaGetSymbolAddress failed with CUDA error %lld", (int)e);
+        return (int)e;
+      }
+      g_static_ptr[device] = static_cast<float*>(p);
+    }
+    scratch = g_static_ptr[device];
+  }
+  const int split = mf_attention_decode_split(hd);
+  const long long splits = (max_ctx + split - 1) / split;
+  float* part_o = scratch;
+  float* part_ml = scratch + (long long)n_tokens * n_heads * splits * hd;
+  return mf_attention_decode(q, k_pool, v_pool, out, part_o, part_ml, n_tokens, n_heads, n_kv, hd, positions,
+                             seq_of_token, block_table, bt_stride, page_size, scale, window, max_ctx, stream);
+}
