@@ -214,6 +214,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=LLAMA_1B["num_hidden_layers"])
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch")
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="decode / prefill: run just that part and print a short line (for profiling small cases)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -235,8 +238,9 @@ def main() -> int:
         model_dir = mf.write_random_model(os.path.join(tmp, "llama_1b_random"), config_from_json(cfg_json), seed=0,
                                           dtype="bfloat16")
         ctx = args.context
-        engine = mf.Engine(model_spec=model_dir, dtype="bfloat16", kv_pool_tokens=64 * (ctx + 64), max_running=64,
-                           token_budget=8192, prefill_chunk=2048)
+        pool_seqs = 64 if args.only == "all" and not args.skip_points else max(args.batch, 1)
+        engine = mf.Engine(model_spec=model_dir, dtype="bfloat16", kv_pool_tokens=pool_seqs * (ctx + 64),
+                           max_running=64, token_budget=8192, prefill_chunk=2048)
         print(f"[bench] model written and loaded in {time.time() - t0:.0f}s", file=sys.stderr, flush=True)
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
@@ -248,11 +252,21 @@ def main() -> int:
     weight_bytes = engine.model.weight_bytes()
     kv_per_token = engine.model.cache_layout.bytes_per_token(2)
 
+    if args.only == "prefill":
+        t_pre = prefill_device(engine, PREFILL_TOKENS, runs=max(1, args.steps), warmup=args.warmup)
+        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(t_pre * 1e3, 3),
+                          "layers": args.layers}))
+        return 0
+    BATCH_ = args.batch
     clocks = ClockSampler()
     clocks.start()
-    sec, launches, kv_tokens = decode_device(engine, BATCH, ctx, args.steps, args.warmup)
+    sec, launches, kv_tokens = decode_device(engine, BATCH_, ctx, args.steps, args.warmup)
     clk = clocks.stop()
-    value = BATCH / sec
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "batch": BATCH_, "context": ctx, "layers": args.layers,
+                          "ms_per_step": round(sec * 1e3, 4), "launches_per_step": launches}))
+        return 0
+    value = BATCH_ / sec
     bytes_step = weight_bytes + kv_tokens * kv_per_token
     achieved = bytes_step / sec / 1e9
 
@@ -272,17 +286,17 @@ def main() -> int:
     prefill = {"value": round(T / t_pre, 1), "tokens": T, "ms": round(t_pre * 1e3, 3),
                "frac": round(flops / t_pre / (pk["bf16_tflops"] * 1e12), 4)}
 
-    e2e_value, h2d, d2h = decode_e2e(engine, BATCH, ctx, args.steps, args.warmup)
+    e2e_value, h2d, d2h = decode_e2e(engine, BATCH_, ctx, args.steps, args.warmup)
 
     line = {
-        "metric": "decode tok/s @ batch 8 (Llama-3.2-1B bf16)", "value": round(value, 1), "unit": "tokens/s",
+        "metric": f"decode tok/s @ batch {BATCH_} (Llama-3.2-1B bf16)", "value": round(value, 1), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded normal(0, 0.02) weights, seeded uniform token ids, random cache contents",
         "config": {
             "model": "Llama-3.2-1B shape (LlamaForCausalLM)", "layers": L, "layers_of_named_config": 16,
             "hidden": H, "heads": nh, "kv_heads": nkv, "head_dim": hd, "intermediate": I, "vocab": V,
-            "global_batch": BATCH, "seq_len": ctx, "context_len": ctx, "kv_block": engine.cache.page_size,
+            "global_batch": BATCH_, "seq_len": ctx, "context_len": ctx, "kv_block": engine.cache.page_size,
             "prefill_tokens": T, "parallelism": "single GPU",
             "l2": "working set per step (weights + live cache) exceeds L2 many times; no flush needed",
             "peaks": pk["source"],

@@ -101,6 +101,30 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
                                          page_size, scale, window, _stream()), "attention_generic")
 
 
+def skinny_max_rows() -> int:
+    return int(library().mf_skinny_max_rows())
+
+
+def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the few-row product kernel takes these operands."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def skinny_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
+    """out = x @ w^T for at most ``skinny_max_rows()`` rows of bfloat16 x (out bfloat16
+    or float32); with ``swiglu`` the rows of w interleave gate and up in groups of 8
+    and out [M, N/2] is silu(gate) * up."""
+    _need_cuda(x, w, out)
+    M, K = x.shape
+    N = w.shape[0]
+    want = (M, N // 2) if swiglu else (M, N)
+    if w.shape[1] != K or tuple(out.shape) != want:
+        raise KernelError(f"skinny_linear: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    check(library().mf_skinny_linear(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out), M, N, K,
+                                     1 if swiglu else 0, _stream()), "skinny_linear")
+
+
 def attention_decode_split(head_dim: int) -> int:
     """Keys per split of the decode kernel for a head size."""
     return int(library().mf_attention_decode_split(head_dim))

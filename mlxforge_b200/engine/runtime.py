@@ -25,7 +25,8 @@ class Runtime:
         self.precise = dtype == torch.float32
         self._buffers: Dict[str, torch.Tensor] = {}
         # rows at or below which the bfloat16 product runs the skinny kernel
-        self.skinny_max_rows = 0
+        self.skinny_max_rows = 16
+        self.skinny_enabled = True
 
     # ------------------------------------------------------------------ scratch
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -53,12 +54,25 @@ class Runtime:
             return out
         if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             raise ops.KernelError(f"linear: operand dtypes {x.dtype} x {w.dtype} are not a supported pair")
-        M = x.shape[0]
-        if M <= self.skinny_max_rows:
+        if self._skinny(x, w):
             ops.skinny_linear(x, w, out)
             return out
         if out.dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)
         else:
             torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+        return out
+
+    def _skinny(self, x, w) -> bool:
+        return self.skinny_enabled and x.shape[0] <= self.skinny_max_rows and ops.skinny_ok(x, w)
+
+    def linear_swiglu(self, x: torch.Tensor, w_gu: torch.Tensor, group: int, out: torch.Tensor) -> torch.Tensor:
+        """``out = silu(x Wg^T) * (x Wu^T)`` for a matrix whose rows interleave gate and
+        up in groups of ``group``.  Few bfloat16 rows: one kernel with the product in
+        its epilogue; otherwise the product, then the elementwise kernel."""
+        if group == 8 and w_gu.shape[0] % 16 == 0 and self._skinny(x, w_gu):
+            ops.skinny_linear(x, w_gu, out, swiglu=True)
+            return out
+        gu = self.linear(x, w_gu, self.buffer("ffn.gu", (x.shape[0], w_gu.shape[0])))
+        ops.swiglu(gu, out, group)
         return out

@@ -45,7 +45,5 @@ class SwiGLU(FeedForward):
     def forward(self, x, batch):
         rt = self.rt
         T = x.shape[0]
-        gu = rt.linear(x, self.w_gu, rt.buffer("ffn.gu", (T, 2 * self.inter)))
-        act = rt.buffer("ffn.act", (T, self.inter))
-        ops.swiglu(gu, act, self.group)
+        act = rt.linear_swiglu(x, self.w_gu, self.group, rt.buffer("ffn.act", (T, self.inter)))
         return rt.linear(act, self.w_down, rt.buffer("ffn.delta", (T, self.hidden)))

@@ -305,3 +305,59 @@ def test_rope_kv_write(dtype, nh, nkv, hd, rot):
     untouched = ~written                      # pools are [page][kv head][slot][channel]
     assert np.all(kp.transpose(0, 2, 1, 3)[untouched] == 0) and np.all(vp.transpose(0, 2, 1, 3)[untouched] == 0), \
         "nothing else in the pools was touched"
+
+
+# ----------------------------------------------------------------------------- few-row products
+
+@pytest.mark.parametrize("M,N,K", [(1, 304, 80), (8, 2048, 2048), (5, 307, 136), (16, 96, 200), (9, 1000, 64),
+                                   (32, 48, 72), (3, 128256, 64), (8, 16, 8192)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_skinny_linear(M, N, K, out_dtype):
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(M * 1000 + N)
+    x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    w = bf16_round(rng.standard_normal((N, K)).astype(np.float32))
+    out = torch.full((M, N), float("nan"), dtype=torch_dtype(out_dtype), device="cuda")
+    ops.skinny_linear(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out)
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    # float32 accumulation of exact bfloat16 products; then one rounding to the output type
+    tol = 3e-6 * np.sqrt(K) * 4 if out_dtype == "float32" else 2.0 ** -8 * np.abs(want).max() + 1e-3
+    assert np.max(np.abs(host(out) - want)) < tol
+    # a row's result does not depend on the other rows
+    if M > 1:
+        out1 = torch.empty((1, N), dtype=torch_dtype(out_dtype), device="cuda")
+        ops.skinny_linear(dev(x[M - 1:M], torch.bfloat16), dev(w, torch.bfloat16), out1)
+        assert torch.equal(out1[0], out[M - 1])
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 136, 80), (8, 8192, 2048), (13, 64, 96)])
+def test_skinny_swiglu(M, I, K):
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(I)
+    x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    wg = bf16_round(rng.standard_normal((I, K)).astype(np.float32) * 0.2)
+    wu = bf16_round(rng.standard_normal((I, K)).astype(np.float32) * 0.2)
+    gu = np.stack([wg.reshape(I // 8, 8, K), wu.reshape(I // 8, 8, K)], axis=1).reshape(2 * I, K)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.skinny_linear(dev(x, torch.bfloat16), dev(gu, torch.bfloat16), out, swiglu=True)
+    g = x.astype(np.float64) @ wg.astype(np.float64).T
+    u = x.astype(np.float64) @ wu.astype(np.float64).T
+    want = g / (1 + np.exp(-g)) * u
+    assert np.all(np.abs(host(out) - want) <= 2.0 ** -7 * (np.abs(want) + 1e-2))
+
+
+def test_skinny_refuses_what_it_cannot_do():
+    import torch
+    from mlxforge_b200.csrc import ops
+    from mlxforge_b200.csrc.binding import KernelError
+    x = torch.zeros((2, 12), dtype=torch.bfloat16, device="cuda")      # K not a multiple of 8
+    w = torch.zeros((16, 12), dtype=torch.bfloat16, device="cuda")
+    assert not ops.skinny_ok(x, w)
+    with pytest.raises(KernelError, match="refused"):
+        ops.skinny_linear(x, w, torch.zeros((2, 16), dtype=torch.bfloat16, device="cuda"))
+    x = torch.zeros((40, 16), dtype=torch.bfloat16, device="cuda")     # too many rows
+    with pytest.raises(KernelError, match="refused"):
+        ops.skinny_linear(x, torch.zeros((16, 16), dtype=torch.bfloat16, device="cuda"),
+                          torch.zeros((40, 16), dtype=torch.bfloat16, device="cuda"))
