@@ -82,6 +82,7 @@ class Engine:
                                                    rope_scaling=config.rope_scaling or None)
         rt = self.model.rt
         rt.skinny_enabled = bool(config.skinny_mm)
+        rt.reserve_rows = config.token_budget
         elt = 4 if dtype == torch.float32 else 2
         per_token = max(1, self.model.cache_layout.bytes_per_token(elt))
         tokens = config.kv_pool_tokens if config.kv_pool_tokens > 0 else config.kv_pool_bytes // per_token

@@ -38,7 +38,7 @@ def make_runner(model_dir: str, dtype, max_tokens: int, page_size: int = REPLAY_
     # whole pages of 16 always suffice for max_tokens
     cache = CacheManager(model.cache_layout, page_size=page_size, max_tokens=max_tokens, max_seqs=max_seqs,
                          dtype=parse_dtype(dtype), device=str(model.rt.device))
-    return ModelRunner(model, cache, model.rt)
+    return ModelRunner(model, cache, model.rt, cuda_graphs=True)
 
 
 def replay(runner: ModelRunner, lines: IO[str], out_dir: str, done: IO[str] = sys.stdout) -> None:

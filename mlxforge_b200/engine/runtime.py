@@ -24,6 +24,10 @@ class Runtime:
         self.device = torch.device(device)
         self.precise = dtype == torch.float32
         self._buffers: Dict[str, torch.Tensor] = {}
+        # bumped whenever a scratch buffer moves: captured CUDA graphs hold the old addresses
+        self.generation = 0
+        # rows every per-token buffer is first made for, so that later, larger steps do not move it
+        self.reserve_rows = 0
         # rows at or below which the bfloat16 product runs the skinny kernel
         self.skinny_max_rows = 16
         self.skinny_enabled = True
@@ -39,8 +43,12 @@ class Runtime:
         key = f"{name}:{dtype}"
         buf = self._buffers.get(key)
         if buf is None or buf.numel() < n:
-            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            cap = n
+            if len(shape) >= 2 and self.reserve_rows > shape[0]:
+                cap = n // int(shape[0]) * self.reserve_rows
+            buf = torch.empty(max(cap, 1), dtype=dtype, device=self.device)
             self._buffers[key] = buf
+            self.generation += 1
         return buf[:n].view(shape)
 
     # ------------------------------------------------------------------ products

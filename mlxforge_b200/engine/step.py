@@ -86,6 +86,10 @@ class ModelRunner:
         self._copy_pending = False
         self.last_meta_bytes = 0
         self.steps = 0
+        # CUDA graphs of decode-only steps, keyed by the shape of the step's metadata
+        self._graphs: Dict[tuple, tuple] = {}
+        self._warm: set = set()
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
@@ -111,15 +115,46 @@ class ModelRunner:
             if lo < 0 or hi >= self.vocab:
                 raise IndexError(f"token id {lo if lo < 0 else hi} is outside the vocabulary [0, {self.vocab})")
         self.cache.reserve([(e.seq, len(e.tokens)) for e in entries])
-        batch = self._build(entries)
-        logits = self.model.forward(batch, self.cache)
+        graphed = self.cuda_graphs and all(len(e.tokens) == 1 for e in entries)
+        batch = self._build(entries, pad_tables=graphed)
+        logits = self._forward_graphed(batch) if graphed else self.model.forward(batch, self.cache)
         for e in entries:
             self.cache.commit(e.seq, len(e.tokens))
         self.steps += 1
         return logits
 
     # ------------------------------------------------------------------ metadata
-    def _build(self, entries: Sequence[StepEntry]) -> StepBatch:
+    def _forward_graphed(self, batch: StepBatch) -> Optional[torch.Tensor]:
+        """Decode-only steps replay a CUDA graph: the kernels read tokens, positions and
+        block tables from the metadata buffer, whose layout is fixed by the key, so a
+        replay needs no host work beyond the one copy of that buffer.  The first step of
+        a shape runs eagerly (it sizes the scratch), the second is captured."""
+        from ..csrc import binding
+        key = (batch.n_seqs, batch.n_wanted, tuple(t.shape[1] for t in batch._block_tables.values()))
+        entry = self._graphs.get(key)
+        if entry is not None and entry[0] == (self.rt.generation, self._meta.data_ptr()):
+            entry[1].replay()
+            binding.count_launches(entry[3])
+            self.graph_replays += 1
+            return entry[2]
+        if key not in self._warm:
+            self._warm.add(key)
+            return self.model.forward(batch, self.cache)
+        if len(self._graphs) >= 64:
+            self._graphs.clear()
+        graph = torch.cuda.CUDAGraph()
+        before = binding.launch_count()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(batch, self.cache)
+        nodes = binding.launch_count() - before
+        binding.count_launches(-nodes)          # capturing launched nothing
+        self._graphs[key] = ((self.rt.generation, self._meta.data_ptr()), graph, logits, nodes)
+        graph.replay()
+        binding.count_launches(nodes)
+        self.graph_replays += 1
+        return logits
+
+    def _build(self, entries: Sequence[StepEntry], pad_tables: bool = False) -> StepBatch:
         order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
@@ -154,6 +189,10 @@ class ModelRunner:
         tables = []
         for g in range(len(self.cache.pools)):
             width = max(1, max(len(entries[i].seq.blocks[g]) for i in order))
+            if pad_tables:
+                # a graph serves every step whose tables fit its width: powers of two from 16 up
+                width = max(16, 1 << (width - 1).bit_length())
+                b.max_ctx = max(b.max_ctx, width * self.cache.page_size)
             tab = np.full((R, width), -1, dtype=np.int32)
             for row, i in enumerate(order):
                 blocks = entries[i].seq.blocks[g]
