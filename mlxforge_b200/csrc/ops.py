@@ -101,6 +101,23 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
                                          page_size, scale, window, _stream()), "attention_generic")
 
 
+def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                      seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, seq_ctx_len: torch.Tensor,
+                      table_row0: int, max_q_len: int, block_table: torch.Tensor, page_size: int, n_heads: int,
+                      n_kv: int, head_dim: int, scale: float, window: int) -> None:
+    """Attention of prompt portions, bfloat16.  ``q`` / ``out`` are the whole step's
+    [T, n_heads*head_dim]; the three per-sequence arrays describe the sequences
+    that start at row ``table_row0`` of ``block_table``."""
+    _need_cuda(q, k_pool, v_pool, out, seq_q_start, seq_q_len, seq_ctx_len, block_table)
+    if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill: bfloat16 only")
+    check(library().mf_attention_prefill(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+                                         seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_ctx_len.data_ptr(),
+                                         table_row0, seq_q_len.shape[0], max_q_len, n_heads, n_kv, head_dim,
+                                         block_table.data_ptr(), block_table.shape[1], page_size, scale, window,
+                                         _stream()), "attention_prefill")
+
+
 def skinny_max_rows() -> int:
     return int(library().mf_skinny_max_rows())
 

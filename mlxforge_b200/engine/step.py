@@ -249,7 +249,11 @@ class ModelRunner:
                                  self.rt.buffer("attn.part_ml", (n_ml,), torch.float32),
                                  batch.positions[:nd], batch.seq_of_token[:nd], table, lane.page_size, n_heads,
                                  need.n_kv_heads, need.head_dim, scale, window, batch.max_ctx)
-        if nd < batch.n_tokens:
+        if nd < batch.n_tokens and q.dtype == torch.bfloat16:
+            ops.attention_prefill(q, lane.k, lane.v, out, batch.seq_q_start[nd:], batch.seq_q_len[nd:],
+                                  batch.seq_ctx_len[nd:], nd, max(batch.q_len[nd:]), table, lane.page_size,
+                                  n_heads, need.n_kv_heads, need.head_dim, scale, window)
+        elif nd < batch.n_tokens:
             ops.attention_generic(q[nd:], lane.k, lane.v, out[nd:], batch.positions[nd:],
                                   batch.seq_of_token[nd:], table, lane.page_size, n_heads, need.n_kv_heads,
                                   need.head_dim, scale, window)

@@ -361,3 +361,37 @@ def test_skinny_refuses_what_it_cannot_do():
     with pytest.raises(KernelError, match="refused"):
         ops.skinny_linear(x, torch.zeros((16, 16), dtype=torch.bfloat16, device="cuda"),
                           torch.zeros((40, 16), dtype=torch.bfloat16, device="cuda"))
+
+
+# ----------------------------------------------------------------------------- prefill attention
+
+@pytest.mark.parametrize("case", ATTN_CASES)
+def test_attention_prefill(case):
+    """Portions of several sequences in one launch: a whole prompt, the tail of a
+    longer context, a two-token portion; checked row by row against the plain formula."""
+    import torch
+    from mlxforge_b200.csrc import ops
+    nh, nkv, hd, lengths, window = case
+    pc = Paged(lengths, nkv, hd, dtype="bfloat16", seed=hd + 2)
+    rng = np.random.default_rng(8)
+    # per sequence: how many of its last tokens are the new ones
+    q_lens = [n if i == 0 else (2 if i == 1 else min(n, 67)) for i, n in enumerate(lengths)]
+    q_lens = [min(ql, n) for ql, n in zip(q_lens, lengths)]
+    starts = np.cumsum([3] + q_lens[:-1]).astype(np.int32)        # 3 unrelated rows come first
+    T = 3 + sum(q_lens)
+    q = bf16_round(rng.standard_normal((T, nh, hd)).astype(np.float32))
+    out = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    scale = hd ** -0.5
+    # a table with one more leading row than sequences, to exercise table_row0
+    table = np.concatenate([np.full((1, pc.table.shape[1]), -1, dtype=np.int32), pc.table])
+    ops.attention_prefill(dev(q.reshape(T, -1), torch.bfloat16), pc.k_pool, pc.v_pool, out, dev(starts),
+                          dev(np.array(q_lens, dtype=np.int32)), dev(np.array(lengths, dtype=np.int32)), 1,
+                          max(q_lens), dev(table), pc.page, nh, nkv, hd, scale, window)
+    got = host(out).reshape(T, nh, hd)
+    assert np.isnan(got[:3]).all(), "rows that belong to no portion are left alone"
+    for s, (n, ql) in enumerate(zip(lengths, q_lens)):
+        for j in range(ql):
+            pos = n - ql + j
+            want = pc.reference(q[starts[s] + j], s, pos, scale, window)
+            d = np.max(np.abs(got[starts[s] + j] - want))
+            assert d < 1.5e-2, (s, j, pos, d)
