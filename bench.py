@@ -185,9 +185,11 @@ def decode_e2e(engine, batch, ctx, steps, warmup):
     import mlxforge_b200 as mf
     rng = np.random.default_rng(2)
     vocab = engine.model.spec.vocab_size
-    plen = ctx - (warmup + steps) - 1
-    reqs = [engine.submit_ids(rng.integers(0, vocab, size=plen).tolist(), mf.GREEDY, warmup + steps + 1, eos_ids=[])
-            for _ in range(batch)]
+    # requests finish their prompts in different steps: every one gets room to decode through
+    # the whole timed region, and is cancelled after it
+    plen = ctx - (warmup + steps) - 1 - 2 * batch
+    reqs = [engine.submit_ids(rng.integers(0, vocab, size=plen).tolist(), mf.GREEDY,
+                              warmup + steps + 4 * batch + 64, eos_ids=[]) for _ in range(batch)]
     while any(len(r.output_ids) < 1 for r in reqs):          # prefill and first token, untimed
         engine.step()
     for _ in range(warmup):
@@ -201,6 +203,9 @@ def decode_e2e(engine, batch, ctx, steps, warmup):
     t1 = time.perf_counter()
     n1 = sum(len(r.output_ids) for r in reqs)
     h2d = engine.runner.last_meta_bytes
+    assert all(not r.finished for r in reqs), "a request ended inside the timed region"
+    for r in reqs:
+        r.cancel()
     engine.run_until_idle()
     return (n1 - n0) / (t1 - t0), h2d, batch * 4
 

@@ -21,6 +21,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..parts.base import FixedState, PagedKV
@@ -114,7 +115,8 @@ class CacheManager:
         slot = self.slots.take()
         for st in self._state:
             st[:, slot].zero_()
-        seq = SequenceCache(seq_id=self._next_id, slot=slot, blocks=[[] for _ in self.layout.paged])
+        seq = SequenceCache(seq_id=self._next_id, slot=slot, blocks=[[] for _ in self.layout.paged],
+                            block_rows=[np.full(16, -1, dtype=np.int32) for _ in self.layout.paged])
         self._next_id += 1
         self._live[seq.seq_id] = seq
         return seq
@@ -153,7 +155,7 @@ class CacheManager:
         for (seq, _), p in zip(requests, per):
             for g, n in enumerate(p):
                 if n:
-                    seq.blocks[g].extend(self.pools[g].take(n, g))
+                    seq._extend(g, self.pools[g].take(n, g))
 
     def commit(self, seq: SequenceCache, n_new: int) -> None:
         """The step wrote ``n_new`` tokens: move the length on and give back pages
@@ -166,6 +168,7 @@ class CacheManager:
             if gone:
                 for b in range(min(first, len(blocks))):
                     blocks[b] = -1
+                seq.block_rows[g][:min(first, len(blocks))] = -1
                 self.pools[g].give_back(gone)
 
     def close(self, seq: SequenceCache) -> None:

@@ -12,6 +12,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
+import numpy as np
+
 
 class OutOfPages(RuntimeError):
     """A reservation that the pool cannot serve.  Nothing was taken."""
@@ -108,6 +110,21 @@ class SequenceCache:
     length: int = 0
     blocks: List[List[int]] = field(default_factory=list)   # [group][logical block] -> page or -1
     closed: bool = False
+    # int32 copies of `blocks`, kept by the manager, so that a step's block table is a memcpy
+    block_rows: List[np.ndarray] = field(default_factory=list)
+
+    def row(self, group: int) -> np.ndarray:
+        return self.block_rows[group][:len(self.blocks[group])]
+
+    def _extend(self, group: int, pages: List[int]) -> None:
+        have = len(self.blocks[group])
+        arr = self.block_rows[group]
+        if have + len(pages) > arr.shape[0]:
+            grown = np.full(max(2 * arr.shape[0], have + len(pages), 16), -1, dtype=np.int32)
+            grown[:have] = arr[:have]
+            self.block_rows[group] = arr = grown
+        arr[have:have + len(pages)] = pages
+        self.blocks[group].extend(pages)
 
     def pages_held(self, group: int) -> int:
         return sum(1 for p in self.blocks[group] if p >= 0)

@@ -17,7 +17,6 @@
 
 namespace {
 
-constexpr int WARPS = 4;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
@@ -48,25 +47,33 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-// keys per warp by head size: the tile of one warp is KPW x (hd + 8) x 2 (K and V) bf16
-template <int HD_MAX> struct Tile { static constexpr int KPW = HD_MAX <= 64 ? 64 : (HD_MAX <= 128 ? 32 : 16); };
+// Keys per warp and tile by head size: a tile is WARPS * KPW keys, staged twice (double
+// buffer) as [WARPS][K, V][KPW][hd + 8] bfloat16.  A block walks SPLIT_KEYS keys.
+template <int HD_MAX> struct Tile {
+  static constexpr int KPW = HD_MAX <= 64 ? 32 : 16;
+  static constexpr int W = 4;                        // warps per block
+};
+constexpr int SPLIT_KEYS = 512;
+constexpr int NSTAGE = 2;               // tiles in flight per warp: NSTAGE - 1 while one is multiplied
 
 template <int HD_MAX>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(Tile<HD_MAX>::W * 32)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                    const __nv_bfloat16* __restrict__ v_pool, float* __restrict__ part_o,
                    float* __restrict__ part_ml, const int* __restrict__ positions,
                    const int* __restrict__ seq_of_token, PagedView pv, int n_heads, float scale_log2,
                    int window, int max_splits) {
   constexpr int KPW = Tile<HD_MAX>::KPW;
-  constexpr int SPLIT = KPW * WARPS;
-  constexpr int NT = KPW / 8;           // score n-tiles per warp
+  constexpr int WARPS = Tile<HD_MAX>::W;
+  constexpr int TILE = KPW * WARPS;
+  constexpr int NT = KPW / 8;           // score n-tiles per warp and tile
   constexpr int DT = HD_MAX / 8;        // output n-tiles (channels / 8)
+  constexpr int KS = HD_MAX / 16;       // k-steps of the score product
   const int hd = pv.head_dim;
   const int ld = hd + 8;                // padded row: conflict-free ldmatrix for every hd % 16 == 0
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [16][ld]
-  __nv_bfloat16* kv_s = q_s + 16 * ld;                                              // [WARPS][2][KPW][ld]
+  __nv_bfloat16* kv_s = q_s + 16 * ld;                                              // [NSTAGE][WARPS][2][KPW][ld]
 
   const int split = blockIdx.x, t = blockIdx.z;
   const int G = n_heads / pv.n_kv_heads;
@@ -76,115 +83,164 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int n_rows = min(16, G - hg * 16);
   const int pos = positions[t], seq = seq_of_token[t];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int k_begin = split * SPLIT;
-  if (k_begin > pos || k_begin + SPLIT <= lo) return;       // nothing visible in this split
+  const int k_begin = split * SPLIT_KEYS;
+  if (k_begin > pos || k_begin + SPLIT_KEYS <= lo) return;       // nothing visible in this split
+  // tiles of this split that hold visible keys
+  const int tile0 = max(k_begin, lo) / TILE, tile1 = min(k_begin + SPLIT_KEYS - 1, pos) / TILE;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = hd >> 3;            // 16-byte pieces per row
 
-  // ---- stage q (rows beyond the group are zero) and this warp's keys and values
+  // a warp copies its own KPW keys and values of a tile; one table lookup per 16 keys
+  auto load_tile = [&](int tile, int stage) {
+    __nv_bfloat16* k_s = kv_s + ((stage * WARPS + warp) * 2 + 0) * KPW * ld;
+    __nv_bfloat16* v_s = k_s + KPW * ld;
+    const int w_begin = tile * TILE + warp * KPW;
+    long long gran_off = 0;
+    {
+      const int key16 = w_begin + lane * 16;
+      if (lane < KPW / 16 && key16 <= pos && key16 + 16 > lo) gran_off = granule_offset(pv, seq, key16, kvh);
+    }
+    for (int i = lane; i < KPW * chunks; i += 32) {
+      const int r = i / chunks, c = i - r * chunks;
+      const int key = w_begin + r;
+      const bool valid = key >= lo && key <= pos;
+      const long long off = __shfl_sync(0xffffffffu, gran_off, r >> 4) + (r & 15) * hd + c * 8;
+      cp_async_16(k_s + r * ld + c * 8, k_pool + (valid ? off : 0), valid);
+      cp_async_16(v_s + r * ld + c * 8, v_pool + (valid ? off : 0), valid);
+    }
+  };
+
+  // ---- stage q (rows beyond the group are zero) with the first tile
   for (int i = threadIdx.x; i < 16 * chunks; i += WARPS * 32) {
     const int r = i / chunks, c = i - r * chunks;
     cp_async_16(q_s + r * ld + c * 8, q + ((long long)t * n_heads + head0 + min(r, n_rows - 1)) * hd + c * 8,
                 r < n_rows);
   }
-  __nv_bfloat16* k_s = kv_s + (warp * 2 + 0) * KPW * ld;
-  __nv_bfloat16* v_s = kv_s + (warp * 2 + 1) * KPW * ld;
-  const int w_begin = k_begin + warp * KPW;
-  for (int i = lane; i < KPW * chunks; i += 32) {
-    const int r = i / chunks, c = i - r * chunks;
-    const int key = w_begin + r;
-    const bool valid = key >= lo && key <= pos;
-    long long off = 0;
-    if (valid) off = paged_offset(pv, seq, key, kvh) + c * 8;
-    cp_async_16(k_s + r * ld + c * 8, k_pool + off, valid);
-    cp_async_16(v_s + r * ld + c * 8, v_pool + off, valid);
+  // prologue: NSTAGE - 1 tiles on their way (an empty group where the split has fewer)
+#pragma unroll
+  for (int p = 0; p < NSTAGE - 1; p++) {
+    if (tile0 + p <= tile1) load_tile(tile0 + p, p);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
   }
-  cp_async_wait_all();
-  __syncthreads();
 
   const int g = lane >> 2, tq = lane & 3;
   float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
   float o[DT][4];
 #pragma unroll
   for (int d = 0; d < DT; d++) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+  unsigned qa[KS][4];                    // the query tile as A fragments, read once
 
-  if (w_begin <= pos && w_begin + KPW > lo) {
-    // ---- scores S[16 x KPW] = Q K^T
-    float s[NT][4];
+  for (int tile = tile0; tile <= tile1; tile++) {
+    const int stage = (tile - tile0) % NSTAGE;
+    if (tile + NSTAGE - 1 <= tile1) load_tile(tile + NSTAGE - 1, (tile - tile0 + NSTAGE - 1) % NSTAGE);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(NSTAGE - 1) : "memory");
+    if (tile == tile0) {
+      __syncthreads();                   // q came from all warps
 #pragma unroll
-    for (int j = 0; j < NT; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      for (int kk = 0; kk < KS; kk++)
+        if (kk * 16 < hd) ldmatrix_x4(qa[kk], q_s + (lane & 15) * ld + kk * 16 + (lane >> 4) * 8);
+    } else {
+      __syncwarp();                      // keys and values of a tile are the warp's own
+    }
+    const __nv_bfloat16* k_s = kv_s + ((stage * WARPS + warp) * 2 + 0) * KPW * ld;
+    const __nv_bfloat16* v_s = k_s + KPW * ld;
+    const int w_begin = tile * TILE + warp * KPW;
+    if (w_begin <= pos && w_begin + KPW > lo) {
+      // ---- scores S[16 x KPW] = Q K^T
+      float s[NT][4];
 #pragma unroll
-    for (int kk = 0; kk < HD_MAX / 16; kk++) {
-      if (kk * 16 < hd) {
+      for (int j = 0; j < NT; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < KS; kk++) {
+        if (kk * 16 < hd) {
+#pragma unroll
+          for (int j = 0; j < NT; j += 2) {
+            unsigned b[4];
+            const int mi = lane >> 3, r = lane & 7;
+            ldmatrix_x4(b, k_s + (j * 8 + (mi >> 1) * 8 + r) * ld + kk * 16 + (mi & 1) * 8);
+            mma_bf16(s[j], qa[kk], b[0], b[1]);
+            mma_bf16(s[j + 1], qa[kk], b[2], b[3]);
+          }
+        }
+      }
+      // ---- scale, mask where the tile crosses an end of the visible range, running softmax
+      const bool edge = w_begin < lo || w_begin + KPW - 1 > pos;
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < NT; j++) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          float v = s[j][e] * scale_log2;
+          if (edge) {
+            const int key = w_begin + j * 8 + tq * 2 + (e & 1);
+            if (key < lo || key > pos) v = -INFINITY;
+          }
+          s[j][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+      float alpha[2], m_use[2];
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m_row[h], mx[h]);
+        m_use[h] = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[h] = (m_row[h] == -INFINITY) ? 0.f : exp2f(m_row[h] - m_use[h]);
+        m_row[h] = m_new;
+      }
+      float sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < NT; j++) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const float p = exp2f(s[j][e] - m_use[e >> 1]);
+          s[j][e] = p;
+          sum[e >> 1] += p;
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
+        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
+        l_row[h] = l_row[h] * alpha[h] + sum[h];
+      }
+#pragma unroll
+      for (int d = 0; d < DT; d++) {
+        o[d][0] *= alpha[0]; o[d][1] *= alpha[0];
+        o[d][2] *= alpha[1]; o[d][3] *= alpha[1];
+      }
+      // ---- O[16 x hd] += P V
+#pragma unroll
+      for (int kk = 0; kk < KPW / 16; kk++) {
         unsigned a[4];
-        ldmatrix_x4(a, q_s + (lane & 15) * ld + kk * 16 + (lane >> 4) * 8);
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-        for (int j = 0; j < NT; j += 2) {
-          unsigned b[4];
-          const int mi = lane >> 3, r = lane & 7;
-          ldmatrix_x4(b, k_s + (j * 8 + (mi >> 1) * 8 + r) * ld + kk * 16 + (mi & 1) * 8);
-          mma_bf16(s[j], a, b[0], b[1]);
-          mma_bf16(s[j + 1], a, b[2], b[3]);
+        for (int d = 0; d < DT; d += 2) {
+          if (d * 8 < hd) {
+            unsigned b[4];
+            const int mi = lane >> 3, r = lane & 7;
+            ldmatrix_x4_trans(b, v_s + (kk * 16 + (mi & 1) * 8 + r) * ld + d * 8 + (mi >> 1) * 8);
+            mma_bf16(o[d], a, b[0], b[1]);
+            mma_bf16(o[d + 1], a, b[2], b[3]);
+          }
         }
       }
     }
-    // ---- mask, softmax statistics of this warp's keys (rows g and g + 8)
-#pragma unroll
-    for (int j = 0; j < NT; j++) {
-#pragma unroll
-      for (int e = 0; e < 4; e++) {
-        const int key = w_begin + j * 8 + tq * 2 + (e & 1);
-        const float v = (key >= lo && key <= pos) ? s[j][e] * scale_log2 : -INFINITY;
-        s[j][e] = v;
-        m_row[e >> 1] = fmaxf(m_row[e >> 1], v);
-      }
-    }
-#pragma unroll
-    for (int h = 0; h < 2; h++) {
-      m_row[h] = fmaxf(m_row[h], __shfl_xor_sync(0xffffffffu, m_row[h], 1));
-      m_row[h] = fmaxf(m_row[h], __shfl_xor_sync(0xffffffffu, m_row[h], 2));
-    }
-    const float m_use[2] = {m_row[0] == -INFINITY ? 0.f : m_row[0], m_row[1] == -INFINITY ? 0.f : m_row[1]};
-#pragma unroll
-    for (int j = 0; j < NT; j++) {
-#pragma unroll
-      for (int e = 0; e < 4; e++) {
-        const float p = exp2f(s[j][e] - m_use[e >> 1]);
-        s[j][e] = p;
-        l_row[e >> 1] += p;
-      }
-    }
-#pragma unroll
-    for (int h = 0; h < 2; h++) {
-      l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 1);
-      l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 2);
-    }
-    // ---- O[16 x hd] = P V
-#pragma unroll
-    for (int kk = 0; kk < KPW / 16; kk++) {
-      unsigned a[4];
-      a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-      a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-      a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-#pragma unroll
-      for (int d = 0; d < DT; d += 2) {
-        if (d * 8 < hd) {
-          unsigned b[4];
-          const int mi = lane >> 3, r = lane & 7;
-          ldmatrix_x4_trans(b, v_s + (kk * 16 + (mi & 1) * 8 + r) * ld + d * 8 + (mi >> 1) * 8);
-          mma_bf16(o[d], a, b[0], b[1]);
-          mma_bf16(o[d + 1], a, b[2], b[3]);
-        }
-      }
-    }
+    __syncwarp();        // the warp is done with this stage before it refills it
   }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
   __syncthreads();     // every warp is done with its keys and values: reuse the space
 
-  // ---- combine the warps: ml_s[WARPS][16][2], o_s[WARPS][16][hd] in float
+  // ---- combine the warps: ml_s[WARPS][16][2], o_s[WARPS][16][hd + 8] in float
   float* ml_s = reinterpret_cast<float*>(kv_s);
   float* o_s = ml_s + WARPS * 16 * 2;
+  const int lo_s = hd + 8;              // row stride that spreads the 8 rows of a store over the banks
   if (tq == 0) {
     ml_s[(warp * 16 + g) * 2 + 0] = m_row[0];
     ml_s[(warp * 16 + g) * 2 + 1] = l_row[0];
@@ -194,10 +250,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
   for (int d = 0; d < DT; d++) {
     if (d * 8 < hd) {
-      float* r0 = o_s + (warp * 16 + g) * hd + d * 8 + tq * 2;
-      float* r1 = o_s + (warp * 16 + g + 8) * hd + d * 8 + tq * 2;
-      r0[0] = o[d][0]; r0[1] = o[d][1];
-      r1[0] = o[d][2]; r1[1] = o[d][3];
+      float* r0 = o_s + (warp * 16 + g) * lo_s + d * 8 + tq * 2;
+      float* r1 = o_s + (warp * 16 + g + 8) * lo_s + d * 8 + tq * 2;
+      *reinterpret_cast<float2*>(r0) = make_float2(o[d][0], o[d][1]);
+      *reinterpret_cast<float2*>(r1) = make_float2(o[d][2], o[d][3]);
     }
   }
   __syncthreads();
@@ -212,7 +268,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       const float mw = ml_s[(w * 16 + r) * 2];
       const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
       L += ml_s[(w * 16 + r) * 2 + 1] * f;
-      acc += o_s[(w * 16 + r) * hd + d] * f;
+      acc += o_s[(w * 16 + r) * lo_s + d] * f;
     }
     const long long row = ((long long)t * n_heads + head0 + r) * max_splits + split;
     part_o[row * hd + d] = acc;
@@ -250,18 +306,21 @@ int launch_decode(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __n
                   const int* positions, const int* seq_of_token, float scale, int window, int max_ctx,
                   cudaStream_t stream) {
   constexpr int KPW = Tile<HD_MAX>::KPW;
-  constexpr int SPLIT = KPW * WARPS;
+  constexpr int WARPS = Tile<HD_MAX>::W;
+  constexpr int SPLIT = SPLIT_KEYS;
   const int hd = pv.head_dim, ld = hd + 8;
   const int max_splits = (max_ctx + SPLIT - 1) / SPLIT;
   const int G = n_heads / pv.n_kv_heads;
   const int hgroups = (G + 15) / 16;
-  const size_t stage = (size_t)(16 * ld + WARPS * 2 * KPW * ld) * sizeof(__nv_bfloat16);
-  const size_t combine = (size_t)16 * ld * sizeof(__nv_bfloat16) + (size_t)WARPS * 16 * (2 + hd) * sizeof(float);
+  const size_t stage = (size_t)(16 * ld + NSTAGE * WARPS * 2 * KPW * ld) * sizeof(__nv_bfloat16);
+  const size_t combine = (size_t)16 * ld * sizeof(__nv_bfloat16) + (size_t)WARPS * 16 * (10 + hd) * sizeof(float);
   const size_t smem = stage > combine ? stage : combine;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          200 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_decode_kernel<HD_MAX>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -281,9 +340,8 @@ int launch_decode(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __n
 
 // Keys per split for a head size (the caller sizes the scratch with it).
 MF_API int mf_attention_decode_split(int hd) {
-  if (hd <= 64) return Tile<64>::KPW * WARPS;
-  if (hd <= 128) return Tile<128>::KPW * WARPS;
-  return Tile<256>::KPW * WARPS;
+  (void)hd;
+  return SPLIT_KEYS;
 }
 
 // Scratch: part_o  [n_tokens * n_heads * max_splits * hd] floats,

@@ -18,8 +18,8 @@
 //     n_tokens * n_heads * ceil(max_ctx / split) * (head_dim + 2) * 4 bytes
 // (mf_attention_decode_static_bytes computes it; split = mf_attention_decode_split(head_dim)).  A
 // call that needs more is refused with MF_ERR_SCRATCH_LIMIT and a message in `err`; nothing is
-// launched.  8 MiB covers, for 32 heads of size 64, 8 sequences at a context of 31,000 tokens or 64
-// sequences at 3,800.
+// launched.  With splits of 512 keys, 8 MiB covers, for 32 heads of size 64, 8 sequences at a
+// context of 63,000 tokens or 64 sequences at 7,600.
 //
 // Set-up.  The first call on each device looks up the array's device address (cudaGetSymbolAddress,
 // with that device current) and remembers it.  Make that first call before any stream capture

@@ -81,14 +81,19 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   auto load_kv = [&](int kt, int stage) {
     __nv_bfloat16* k_s = kv_s + (stage * 2 + 0) * BN * ld;
     __nv_bfloat16* v_s = kv_s + (stage * 2 + 1) * BN * ld;
+    // one block-table lookup per granule of 16 keys (lanes 0..3 of every warp), then shared
+    long long gran_off = 0;
+    {
+      const int key16 = kt * BN + lane * 16;
+      if (lane < BN / 16 && key16 <= pos_last && key16 + 16 > lo_first) gran_off = granule_offset(pv, seq_row, key16, kvh);
+    }
     for (int i = threadIdx.x; i < BN * chunks; i += WARPS * 32) {
       const int r = i / chunks, c = i - r * chunks;
       const int key = kt * BN + r;
       const bool valid = key >= lo_first && key <= pos_last;
-      long long off = 0;
-      if (valid) off = paged_offset(pv, seq_row, key, kvh) + c * 8;
-      cp_async_16(k_s + r * ld + c * 8, k_pool + off, valid);
-      cp_async_16(v_s + r * ld + c * 8, v_pool + off, valid);
+      const long long off = __shfl_sync(0xffffffffu, gran_off, r >> 4) + (r & 15) * hd + c * 8;
+      cp_async_16(k_s + r * ld + c * 8, k_pool + (valid ? off : 0), valid);
+      cp_async_16(v_s + r * ld + c * 8, v_pool + (valid ? off : 0), valid);
     }
   };
 
@@ -236,6 +241,8 @@ int launch_prefill(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          200 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_prefill_kernel<HD_MAX>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }

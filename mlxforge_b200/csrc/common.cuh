@@ -78,3 +78,11 @@ __device__ __forceinline__ long long paged_offset(const PagedView& pv, int seq, 
   const long long page = pv.block_table[(long long)seq * pv.bt_stride + blk];
   return ((page * pv.n_kv_heads + kv_head) * pv.page_size + slot) * (long long)pv.head_dim;
 }
+
+// Offset of the first of 16 consecutive positions [pos16, pos16 + 16), pos16 a multiple
+// of 16: they share a page because the page size is a multiple of 16.  Rows of the
+// granule are head_dim apart.  Kernels look this up once per granule and not once per
+// row, so that no address waits on a load of the block table inside a copy loop.
+__device__ __forceinline__ long long granule_offset(const PagedView& pv, int seq, int pos16, int kv_head) {
+  return paged_offset(pv, seq, pos16, kv_head);
+}

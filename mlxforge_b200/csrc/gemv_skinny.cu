@@ -19,7 +19,6 @@
 namespace {
 
 constexpr int WARPS = 8;
-constexpr int UNROLL = 4;
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
@@ -40,6 +39,7 @@ template <int NB, int ROWS, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, OutT* __restrict__ out,
               int M, int N, int K, int mode) {
+  constexpr int UNROLL = NB >= 4 ? 2 : 4;
   __shared__ float red[WARPS][ROWS][NB * 8 + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * ROWS;
@@ -53,9 +53,12 @@ skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
 #pragma unroll
   for (int nb = 0; nb < NB; nb++) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f;
 
-  // the loop bound is the same for every lane of a warp (mma.sync needs all 32 of them)
-  for (int kb = warp * 32; kb < K; kb += WARPS * 32 * UNROLL) {
-    uint4 a[UNROLL], b[UNROLL], xv[UNROLL][NB];
+  // Two stages of UNROLL loads each are kept in flight: while one stage is multiplied the
+  // next is on its way.  The loop bound is the same for every lane of a warp (mma.sync
+  // needs all 32 of them); a piece beyond K is not read and counts as zero.
+  constexpr int STEP = WARPS * 32 * UNROLL;
+  uint4 a0[UNROLL], b0[UNROLL], x0[UNROLL][NB], a1[UNROLL], b1[UNROLL], x1[UNROLL][NB];
+  auto load = [&](uint4 (&a)[UNROLL], uint4 (&b)[UNROLL], uint4 (&xv)[UNROLL][NB], int kb) {
 #pragma unroll
     for (int u = 0; u < UNROLL; u++) {
       const int k = kb + u * WARPS * 32 + t * 8;
@@ -68,6 +71,8 @@ skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
         xv[u][nb] = (in && m < M) ? __ldg(reinterpret_cast<const uint4*>(x + (long long)m * K + k)) : zero;
       }
     }
+  };
+  auto multiply = [&](const uint4 (&a)[UNROLL], const uint4 (&b)[UNROLL], const uint4 (&xv)[UNROLL][NB]) {
 #pragma unroll
     for (int u = 0; u < UNROLL; u++) {
 #pragma unroll
@@ -76,6 +81,13 @@ skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
         mma_bf16(acc[nb], a[u].z, b[u].z, a[u].w, b[u].w, xv[u][nb].z, xv[u][nb].w);
       }
     }
+  };
+  load(a0, b0, x0, warp * 32);
+  for (int kb = warp * 32; kb < K; kb += 2 * STEP) {
+    load(a1, b1, x1, kb + STEP);
+    multiply(a0, b0, x0);
+    load(a0, b0, x0, kb + 2 * STEP);
+    multiply(a1, b1, x1);
   }
   // ---- sum the 8 warps' partial results in a fixed order
 #pragma unroll

@@ -135,7 +135,7 @@ class Engine:
         try:
             step_entries = []
             for e in entries:
-                ids = e.request.all_ids[e.start:e.start + e.count]
+                ids = e.request.tokens(e.start, e.count)
                 step_entries.append(StepEntry(e.request.seq, ids, [e.count - 1] if e.samples else []))
             logits = self.runner.step(step_entries)
             sampled: List[int] = []

@@ -83,6 +83,21 @@ class Request:
         token can be sampled: the prompt and what was generated so far."""
         return self.prompt_ids + self.output_ids
 
+    @property
+    def n_tokens(self) -> int:
+        """len(all_ids) without building the list."""
+        return len(self.prompt_ids) + len(self.output_ids)
+
+    def tokens(self, start: int, count: int) -> List[int]:
+        """all_ids[start:start + count] without building the whole list."""
+        n_prompt = len(self.prompt_ids)
+        end = start + count
+        if end <= n_prompt:
+            return self.prompt_ids[start:end]
+        if start >= n_prompt:
+            return self.output_ids[start - n_prompt:end - n_prompt]
+        return self.prompt_ids[start:] + self.output_ids[:end - n_prompt]
+
     def emit(self, token: int) -> None:
         if self.first_token_time is None:
             self.first_token_time = time.perf_counter()

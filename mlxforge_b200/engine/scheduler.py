@@ -105,8 +105,9 @@ class Scheduler:
             taken = [0] * n_groups
             ok = True
             # running requests in admission order: decode tokens first
-            decoders = [r for r in self.running if r.computed == len(r.all_ids) - 1 and r.output_ids]
-            prefills = [r for r in self.running if r not in decoders]
+            decoders = [r for r in self.running if r.output_ids and r.computed == r.n_tokens - 1]
+            in_decode = {id(r) for r in decoders}
+            prefills = [r for r in self.running if id(r) not in in_decode]
             for r in decoders:
                 need = self.cache.pages_needed(r.seq, 1)
                 if budget < 1 or not self._pages_fit(taken, need):
@@ -117,7 +118,7 @@ class Scheduler:
                 entries.append(PlannedEntry(r, r.computed, 1, True))
             if ok:
                 for r in prefills:
-                    left = len(r.all_ids) - r.computed
+                    left = r.n_tokens - r.computed
                     n = min(left, cfg.prefill_chunk, budget)
                     if n <= 0:
                         continue
@@ -130,7 +131,7 @@ class Scheduler:
                         need = self.cache.pages_needed(r.seq, n)
                     taken = [a + b for a, b in zip(taken, need)]
                     budget -= n
-                    entries.append(PlannedEntry(r, r.computed, n, r.computed + n == len(r.all_ids)))
+                    entries.append(PlannedEntry(r, r.computed, n, r.computed + n == r.n_tokens))
             if ok and (entries or not self.running):
                 break
             if ok and not entries:
@@ -149,13 +150,13 @@ class Scheduler:
                 self.waiting.popleft()
                 self._finish(r, FINISH_CANCEL)
                 continue
-            total_pages = self.cache.pages_for_tokens(len(r.all_ids) + 1)
+            total_pages = self.cache.pages_for_tokens(r.n_tokens + 1)
             if any(t > cap for t, cap in zip(total_pages, self.cache.total_pages())):
                 self.waiting.popleft()
                 self._finish(r, FINISH_ERROR,
                              f"request needs {max(total_pages)} pages, the pool has {min(self.cache.total_pages())}")
                 continue
-            n = min(len(r.all_ids), cfg.prefill_chunk, budget)
+            n = min(r.n_tokens, cfg.prefill_chunk, budget)
             need = self.cache.pages_for_tokens(n)
             if not self._pages_fit(taken, need):
                 break                                   # stays in waiting until pages are free
@@ -170,7 +171,7 @@ class Scheduler:
             self.running.append(r)
             taken = [a + b for a, b in zip(taken, need)]
             budget -= n
-            entries.append(PlannedEntry(r, 0, n, n == len(r.all_ids)))
+            entries.append(PlannedEntry(r, 0, n, n == r.n_tokens))
         self.metrics.peak_running = max(self.metrics.peak_running, len(self.running))
         return entries
 
@@ -197,7 +198,7 @@ class Scheduler:
             self.cache.close(victim.seq)
             victim.seq = None
             self._finish(victim, FINISH_ERROR,
-                         f"request of {len(victim.all_ids)} tokens does not fit in the cache pool even alone")
+                         f"request of {victim.n_tokens} tokens does not fit in the cache pool even alone")
             return "failed"
         self.running.remove(victim)
         self.cache.close(victim.seq)

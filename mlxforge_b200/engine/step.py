@@ -195,8 +195,8 @@ class ModelRunner:
                 b.max_ctx = max(b.max_ctx, width * self.cache.page_size)
             tab = np.full((R, width), -1, dtype=np.int32)
             for row, i in enumerate(order):
-                blocks = entries[i].seq.blocks[g]
-                tab[row, :len(blocks)] = blocks
+                blocks = entries[i].seq.row(g)
+                tab[row, :blocks.shape[0]] = blocks
             tables.append(tab)
 
         parts = [tokens, positions, seq_of, np.asarray(want, dtype=np.int32),

@@ -93,8 +93,10 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     fn, size = _symbols()
     nh, nkv, hd = 32, 8, 64
     q, k, v, pos, seq, table, _ = _case(3, [40, 50], nh, nkv, hd)
-    too_long = 200000                      # 2 tokens x 32 heads x 782 splits x 66 floats > 8 MiB
-    assert size(2, nh, hd, too_long) > STATIC_BYTES
+    too_long = 64                          # grow the claimed context until the partials no longer fit
+    while size(2, nh, hd, too_long) <= STATIC_BYTES:
+        too_long *= 2
+    assert size(2, nh, hd, too_long // 2) <= STATIC_BYTES < size(2, nh, hd, too_long)
     out = torch.zeros((2, nh * hd), dtype=torch.bfloat16, device="cuda")
     err = ctypes.create_string_buffer(256)
     rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), 2, nh, nkv, hd, pos.data_ptr(),
