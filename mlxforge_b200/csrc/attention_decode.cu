@@ -75,6 +75,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [16][ld]
   __nv_bfloat16* kv_s = q_s + 16 * ld;                                              // [NSTAGE][WARPS][2][KPW][ld]
 
+  pdl_launch();
+  pdl_wait();
   const int split = blockIdx.x, t = blockIdx.z;
   const int G = n_heads / pv.n_kv_heads;
   const int hgroups = (G + 15) / 16;
@@ -283,6 +285,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, const int* __restrict__ positions,
                                          int n_heads, int hd, int window, int max_splits, int split_keys) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const int pos = positions[t];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -325,15 +329,13 @@ int launch_decode(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __n
     configured = true;
   }
   dim3 grid(max_splits, pv.n_kv_heads * hgroups, n_tokens);
-  attn_decode_kernel<HD_MAX><<<grid, WARPS * 32, smem, stream>>>(q, k_pool, v_pool, part_o, part_ml, positions,
-                                                                seq_of_token, pv, n_heads, scale * LOG2E, window,
-                                                                max_splits);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_dep(attn_decode_kernel<HD_MAX>, grid, dim3(WARPS * 32), smem, stream, q, k_pool, v_pool,
+                             part_o, part_ml, positions, seq_of_token, pv, n_heads, scale * LOG2E, window, max_splits);
   if (e != cudaSuccess) return (int)e;
   dim3 mgrid(n_tokens, n_heads);
-  attn_decode_merge_kernel<<<mgrid, hd >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, out, positions, n_heads, hd,
-                                                                       window, max_splits, SPLIT);
-  return (int)cudaGetLastError();
+  return (int)launch_dep(attn_decode_merge_kernel, mgrid, dim3(hd >= 128 ? 128 : 64), 0, stream,
+                         (const float*)part_o, (const float*)part_ml, out, positions, n_heads, hd, window, max_splits,
+                         SPLIT);
 }
 
 }  // namespace

@@ -86,3 +86,31 @@ __device__ __forceinline__ long long paged_offset(const PagedView& pv, int seq, 
 __device__ __forceinline__ long long granule_offset(const PagedView& pv, int seq, int pos16, int kv_head) {
   return paged_offset(pv, seq, pos16, kv_head);
 }
+
+// ---------------------------------------------------------------------------- dependent launch
+// Kernels of the decode step are launched so that the next kernel may start while this
+// one is still running (programmatic dependent launch): a kernel first lets its dependents
+// go (pdl_launch), does what needs no input from its predecessor (fetching weights, which
+// never change), and only then waits for the predecessor to finish (pdl_wait).  Every global
+// read of activations and every global write comes after pdl_wait, so the result is that of
+// running the kernels one after the other.  Under a normal launch both are no-ops.
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+extern int g_mf_pdl;      // 1: launch with the dependent-launch attribute (set by mf_set_pdl)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_mf_pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -7,6 +7,13 @@
 // Sums of squares, angles and the residual stream are 32-bit here.
 #include "common.cuh"
 
+int g_mf_pdl = 1;
+MF_API int mf_set_pdl(int on) {
+  const int old = g_mf_pdl;
+  g_mf_pdl = on ? 1 : 0;
+  return old;
+}
+
 // ------------------------------------------------------------------ embedding
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
@@ -20,6 +27,8 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 // bfloat16 rows in 16-byte pieces (H a multiple of 8)
 __global__ void embed_bf16_vec_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ tokens,
                                       float* __restrict__ out, int H) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const uint4* row = reinterpret_cast<const uint4*>(table + (long long)tokens[t] * H);
   float4* o = reinterpret_cast<float4*>(out + (long long)t * H);
@@ -37,8 +46,8 @@ MF_API int mf_embed(const void* table, int table_dtype, const int* tokens, float
                     cudaStream_t stream) {
   if (T <= 0) return 0;
   if (table_dtype == MF_BF16 && H % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0) {
-    embed_bf16_vec_kernel<<<T, 128, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, H);
-    return (int)cudaGetLastError();
+    return (int)launch_dep(embed_bf16_vec_kernel, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)table, tokens,
+                           out, H);
   }
   if (table_dtype == MF_F32)
     embed_kernel<float><<<T, 256, 0, stream>>>((const float*)table, tokens, out, H);
@@ -89,6 +98,8 @@ add_rmsnorm_bf16_vec_kernel(float* __restrict__ resid, const __nv_bfloat16* __re
                             const float* __restrict__ w, float eps, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ rows, int H) {
   __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
   const int r = blockIdx.x;
   const long long src = rows ? rows[r] : r;
   float* x = resid + src * H;
@@ -147,10 +158,14 @@ MF_API int mf_add_rmsnorm(float* resid, const void* delta, int delta_dtype, cons
       (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) == 0) {
     const __nv_bfloat16* d = (const __nv_bfloat16*)delta;
     __nv_bfloat16* o = (__nv_bfloat16*)out;
-    if (H <= 2048) add_rmsnorm_bf16_vec_kernel<1><<<n_rows, 256, 0, stream>>>(resid, d, w, eps, o, rows, H);
-    else if (H <= 4096) add_rmsnorm_bf16_vec_kernel<2><<<n_rows, 256, 0, stream>>>(resid, d, w, eps, o, rows, H);
-    else add_rmsnorm_bf16_vec_kernel<4><<<n_rows, 256, 0, stream>>>(resid, d, w, eps, o, rows, H);
-    return (int)cudaGetLastError();
+    if (H <= 2048)
+      return (int)launch_dep(add_rmsnorm_bf16_vec_kernel<1>, dim3(n_rows), dim3(256), 0, stream, resid, d, w, eps, o,
+                             rows, H);
+    if (H <= 4096)
+      return (int)launch_dep(add_rmsnorm_bf16_vec_kernel<2>, dim3(n_rows), dim3(256), 0, stream, resid, d, w, eps, o,
+                             rows, H);
+    return (int)launch_dep(add_rmsnorm_bf16_vec_kernel<4>, dim3(n_rows), dim3(256), 0, stream, resid, d, w, eps, o,
+                           rows, H);
   }
   const int threads = H >= 1024 ? 256 : 128;
 #define LAUNCH(TD, TO)                                                                          \
@@ -228,6 +243,8 @@ rope_kv_write_bf16_vec_kernel(const __nv_bfloat16* __restrict__ qkv, int n_heads
                               __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
                               int write_kv) {
   extern __shared__ float cs[];            // [half] cos, [half] sin
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t], seq = seq_of_token[t];
   const int half = rot >> 1;
@@ -291,10 +308,9 @@ MF_API int mf_rope_kv_write(const void* qkv, int dtype, int T, int n_heads, int 
   PagedView pv{block_table, bt_stride, page_size, n_kv, hd};
   if (dtype == MF_BF16 && !precise && rot_dim % 16 == 0 && hd % 8 == 0 &&
       (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0) {
-    rope_kv_write_bf16_vec_kernel<<<T, 256, (size_t)rot_dim * sizeof(float), stream>>>(
-        (const __nv_bfloat16*)qkv, n_heads, n_kv, hd, rot_dim, positions, seq_of_token, pv, freqs,
-        (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, write_kv);
-    return (int)cudaGetLastError();
+    return (int)launch_dep(rope_kv_write_bf16_vec_kernel, dim3(T), dim3(256), (size_t)rot_dim * sizeof(float), stream,
+                           (const __nv_bfloat16*)qkv, n_heads, n_kv, hd, rot_dim, positions, seq_of_token, pv, freqs,
+                           (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, write_kv);
   }
   if (dtype == MF_F32)
     rope_kv_write_kernel<float><<<T, 256, 0, stream>>>((const float*)qkv, n_heads, n_kv, hd, rot_dim, positions,

@@ -58,17 +58,23 @@ skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   // needs all 32 of them); a piece beyond K is not read and counts as zero.
   constexpr int STEP = WARPS * 32 * UNROLL;
   uint4 a0[UNROLL], b0[UNROLL], x0[UNROLL][NB], a1[UNROLL], b1[UNROLL], x1[UNROLL][NB];
-  auto load = [&](uint4 (&a)[UNROLL], uint4 (&b)[UNROLL], uint4 (&xv)[UNROLL][NB], int kb) {
+  auto load_w = [&](uint4 (&a)[UNROLL], uint4 (&b)[UNROLL], int kb) {
 #pragma unroll
     for (int u = 0; u < UNROLL; u++) {
       const int k = kb + u * WARPS * 32 + t * 8;
       const bool in = k < K;
       a[u] = (in && va) ? ldg_stream(wa + k) : zero;
       b[u] = (in && vb) ? ldg_stream(wb + k) : zero;
+    }
+  };
+  auto load_x = [&](uint4 (&xv)[UNROLL][NB], int kb) {
+#pragma unroll
+    for (int u = 0; u < UNROLL; u++) {
+      const int k = kb + u * WARPS * 32 + t * 8;
 #pragma unroll
       for (int nb = 0; nb < NB; nb++) {
         const int m = nb * 8 + g;
-        xv[u][nb] = (in && m < M) ? __ldg(reinterpret_cast<const uint4*>(x + (long long)m * K + k)) : zero;
+        xv[u][nb] = (k < K && m < M) ? __ldg(reinterpret_cast<const uint4*>(x + (long long)m * K + k)) : zero;
       }
     }
   };
@@ -82,12 +88,20 @@ skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
       }
     }
   };
-  load(a0, b0, x0, warp * 32);
+  // weights never change: the first two stages of them are fetched while the kernel that
+  // produces x may still be running; x is read only after it has finished
+  pdl_launch();
+  load_w(a0, b0, warp * 32);
+  load_w(a1, b1, warp * 32 + STEP);
+  pdl_wait();
+  load_x(x0, warp * 32);
   for (int kb = warp * 32; kb < K; kb += 2 * STEP) {
-    load(a1, b1, x1, kb + STEP);
+    load_x(x1, kb + STEP);
     multiply(a0, b0, x0);
-    load(a0, b0, x0, kb + 2 * STEP);
+    load_w(a0, b0, kb + 2 * STEP);
+    load_x(x0, kb + 2 * STEP);
     multiply(a1, b1, x1);
+    load_w(a1, b1, kb + 3 * STEP);
   }
   // ---- sum the 8 warps' partial results in a fixed order
 #pragma unroll
@@ -132,10 +146,10 @@ int launch(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, int
   // few output rows: halve the tile so that there are enough blocks for every SM
   const bool small = mode == 0 && (N + 15) / 16 < 296;
   if (small)
-    skinny_kernel<NB, 8, OutT><<<(N + 7) / 8, WARPS * 32, 0, stream>>>(x, W, out, M, N, K, mode);
-  else
-    skinny_kernel<NB, 16, OutT><<<(N + 15) / 16, WARPS * 32, 0, stream>>>(x, W, out, M, N, K, mode);
-  return (int)cudaGetLastError();
+    return (int)launch_dep(skinny_kernel<NB, 8, OutT>, dim3((N + 7) / 8), dim3(WARPS * 32), 0, stream, x, W, out, M, N,
+                           K, mode);
+  return (int)launch_dep(skinny_kernel<NB, 16, OutT>, dim3((N + 15) / 16), dim3(WARPS * 32), 0, stream, x, W, out, M,
+                         N, K, mode);
 }
 
 template <typename OutT>

@@ -226,3 +226,9 @@ def filter_logits(logits: torch.Tensor, params) -> None:
     dk = torch.from_numpy(ks).to(logits.device)
     check(library().mf_filter_logits(logits.data_ptr(), n, V, logits.stride(0), df[0].data_ptr(), dk.data_ptr(),
                                      df[1].data_ptr(), df[2].data_ptr(), _stream()), "filter_logits")
+
+
+def set_dependent_launch(on: bool) -> bool:
+    """Switch programmatic dependent launch of the decode-path kernels on or off;
+    returns the previous setting.  Results do not depend on it."""
+    return bool(library().mf_set_pdl(1 if on else 0))

@@ -208,3 +208,35 @@ def test_filters_and_penalties_against_plain():
     for r, p in enumerate(pp):
         want = P.apply_penalties(logits[r], hist[r], p.repetition_penalty, p.frequency_penalty, p.presence_penalty)
         assert np.max(np.abs(got[r] - want)) < 1e-5
+
+
+def test_dependent_launch_and_graphs_change_no_bit(tiny):
+    """Decoding with CUDA graphs and dependent launches gives the same logits, bit for
+    bit, as launching every kernel eagerly one after the other."""
+    import torch
+    from mlxforge_b200.csrc import ops
+    from mlxforge_b200.engine.replay import make_runner
+    from mlxforge_b200.engine.step import StepEntry
+    d, cfg, w = tiny["B"]
+    prompts = [random_prompt(cfg, n, 90 + i) for i, n in enumerate([33, 70, 5])]
+
+    def run(graphs, pdl):
+        old = ops.set_dependent_launch(pdl)
+        try:
+            runner = make_runner(d, "bfloat16", 512)
+            runner.cuda_graphs = graphs
+            seqs = [runner.cache.open_sequence() for _ in prompts]
+            runner.step([StepEntry(s, p[:-6], []) for s, p in zip(seqs, prompts)])
+            outs = []
+            for i in range(6, 0, -1):
+                logits = runner.step([StepEntry(s, [p[-i]], [0]) for s, p in zip(seqs, prompts)])
+                outs.append(logits.clone())
+            torch.cuda.synchronize()
+            return torch.stack(outs), runner.graph_replays
+        finally:
+            ops.set_dependent_launch(old)
+
+    eager, n0 = run(False, False)
+    fast, n1 = run(True, True)
+    assert n0 == 0 and n1 >= 4, "the second run must have replayed graphs"
+    assert torch.equal(eager, fast)
