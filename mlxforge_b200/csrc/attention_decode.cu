@@ -75,8 +75,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [16][ld]
   __nv_bfloat16* kv_s = q_s + 16 * ld;                                              // [NSTAGE][WARPS][2][KPW][ld]
 
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int split = blockIdx.x, t = blockIdx.z;
   const int G = n_heads / pv.n_kv_heads;
   const int hgroups = (G + 15) / 16;
@@ -285,8 +285,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, const int* __restrict__ positions,
                                          int n_heads, int hd, int window, int max_splits, int split_keys) {
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x, h = blockIdx.y;
   const int pos = positions[t];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;

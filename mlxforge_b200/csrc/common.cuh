@@ -89,9 +89,10 @@ __device__ __forceinline__ long long granule_offset(const PagedView& pv, int seq
 
 // ---------------------------------------------------------------------------- dependent launch
 // Kernels of the decode step are launched so that the next kernel may start while this
-// one is still running (programmatic dependent launch): a kernel first lets its dependents
-// go (pdl_launch), does what needs no input from its predecessor (fetching weights, which
-// never change), and only then waits for the predecessor to finish (pdl_wait).  Every global
+// one is still running (programmatic dependent launch): a kernel does what needs no
+// input from its predecessor (fetching weights, which never change), waits for the
+// predecessor to finish (pdl_wait) and then lets its own dependents go (pdl_launch): they
+// start while this kernel runs, one kernel ahead and no further.  Every global
 // read of activations and every global write comes after pdl_wait, so the result is that of
 // running the kernels one after the other.  Under a normal launch both are no-ops.
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }

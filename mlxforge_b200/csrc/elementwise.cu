@@ -27,8 +27,8 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 // bfloat16 rows in 16-byte pieces (H a multiple of 8)
 __global__ void embed_bf16_vec_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ tokens,
                                       float* __restrict__ out, int H) {
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x;
   const uint4* row = reinterpret_cast<const uint4*>(table + (long long)tokens[t] * H);
   float4* o = reinterpret_cast<float4*>(out + (long long)t * H);
@@ -98,8 +98,8 @@ add_rmsnorm_bf16_vec_kernel(float* __restrict__ resid, const __nv_bfloat16* __re
                             const float* __restrict__ w, float eps, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ rows, int H) {
   __shared__ float red[32];
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int r = blockIdx.x;
   const long long src = rows ? rows[r] : r;
   float* x = resid + src * H;
@@ -243,8 +243,8 @@ rope_kv_write_bf16_vec_kernel(const __nv_bfloat16* __restrict__ qkv, int n_heads
                               __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
                               int write_kv) {
   extern __shared__ float cs[];            // [half] cos, [half] sin
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x;
   const int pos = positions[t], seq = seq_of_token[t];
   const int half = rot >> 1;

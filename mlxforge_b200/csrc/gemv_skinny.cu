@@ -90,10 +90,11 @@ skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   };
   // weights never change: the first two stages of them are fetched while the kernel that
   // produces x may still be running; x is read only after it has finished
-  pdl_launch();
   load_w(a0, b0, warp * 32);
   load_w(a1, b1, warp * 32 + STEP);
   pdl_wait();
+  pdl_launch();      // only now: a kernel that let its dependents go before waiting would let the
+                     // whole chain of kernels pile up on the SMs, all waiting
   load_x(x0, warp * 32);
   for (int kb = warp * 32; kb < K; kb += 2 * STEP) {
     load_x(x1, kb + STEP);

@@ -218,7 +218,7 @@ def test_dependent_launch_and_graphs_change_no_bit(tiny):
     from mlxforge_b200.engine.replay import make_runner
     from mlxforge_b200.engine.step import StepEntry
     d, cfg, w = tiny["B"]
-    prompts = [random_prompt(cfg, n, 90 + i) for i, n in enumerate([33, 70, 5])]
+    prompts = [random_prompt(cfg, n, 90 + i) for i, n in enumerate([33, 70, 9])]
 
     def run(graphs, pdl):
         old = ops.set_dependent_launch(pdl)
