@@ -76,7 +76,7 @@ class ModelRunner:
 
     def __init__(self, model, cache: CacheManager, runtime, cuda_graphs: bool = False):
         self.model = model
-        self.cuda_graphs = cuda_graphs
+        self.cuda_graphs = cuda_graphs and model.graph_safe
         self.cache = cache
         self.rt = runtime
         self.vocab = model.spec.vocab_size

@@ -44,6 +44,18 @@ class DecoderModel:
         yield self.final_norm
         yield self.head
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether every part (the attention mixers' position encodings included) can be
+        recorded into a CUDA graph."""
+        for p in self.parts():
+            if not getattr(p, "graph_safe", False):
+                return False
+            pos = getattr(p, "position", None)
+            if pos is not None and not getattr(pos, "graph_safe", False):
+                return False
+        return True
+
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs: Dict[str, TensorSpec] = {}
         for p in self.parts():

@@ -21,6 +21,8 @@ from .base import POSITIONS, Mixer, PagedKV, TensorSpec, build_part, register_mi
 
 @register_mixer("attention")
 class AttentionMixer(Mixer):
+    graph_safe = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         p = params

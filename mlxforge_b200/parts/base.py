@@ -109,6 +109,12 @@ CacheNeed = Union[PagedKV, FixedState, None]
 class Part:
     """Common base: construction, tensor declaration, binding."""
 
+    # True if ``forward`` only launches work that a CUDA graph can record and replay:
+    # no host decision that depends on the step's data (lengths, slots), no read-back,
+    # no allocation.  The engine replays decode steps from graphs only when every part
+    # of the model says so; a part that does not say so is simply run eagerly.
+    graph_safe = False
+
     def __init__(self, params: Dict[str, Any], prefix: str, runtime: "Any"):
         self.params = dict(params)
         self.prefix = prefix

@@ -14,6 +14,8 @@ from .base import Part, TensorSpec, register_embedding, register_head
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         self.vocab = int(params["vocab_size"])
@@ -36,6 +38,8 @@ class TokenEmbedding(Part):
 
 @register_head("linear_head")
 class LinearHead(Part):
+    graph_safe = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         self.vocab = int(params["vocab_size"])

@@ -15,6 +15,8 @@ from .base import FeedForward, TensorSpec, register_feed_forward
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         self.hidden = int(params["hidden_size"])

@@ -13,6 +13,8 @@ from .base import Norm, TensorSpec, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         self.size = int(params["size"])

@@ -50,6 +50,8 @@ def rope_frequencies(rotary_dim: int, theta: float, scaling) -> np.ndarray:
 
 @register_position("rope")
 class RotaryEncoding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         self.head_dim = int(params["head_dim"])
@@ -67,6 +69,8 @@ class RotaryEncoding(PositionEncoding):
 
 @register_position("none")
 class NoPositions(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         self.head_dim = int(params["head_dim"])

@@ -1,0 +1,268 @@
+"""Generality of the parts: a toy architecture defined HERE — a mixer with
+fixed-size state of its own, a feed-forward with routing, layers with different
+mixers, a windowed attention layer without position encoding, a schedule that
+runs one layer twice and lets one run read another run's cache — is registered,
+built from a model folder and stepped through the engine's own loader, cache
+manager and step function, with no change to the framework's files.  Its logits,
+in portions and token by token, are compared with a plain NumPy forward of the
+same toy model written below."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import plain_llama as P
+from helpers import bf16_round, write_model_dir
+
+pytestmark = pytest.mark.gpu
+
+H, V, D_STATE, N_EXPERTS, INTER = 48, 97, 24, 3, 40
+NH, NKV, HD, WINDOW = 3, 1, 16, 21
+DECAY = 0.8
+EPS = 1e-5
+
+
+# ----------------------------------------------------------------------------- the toy parts (torch ops: tests may)
+
+def _register():
+    import torch
+    from mlxforge_b200.config.model_config import ModelConfig
+    from mlxforge_b200.config.registry import register_architecture
+    from mlxforge_b200.parts.base import (FeedForward, FixedState, LayerSpec, Mixer, ModelSpec, PartSpec,
+                                          ScheduleItem, TensorSpec, register_feed_forward, register_mixer)
+
+    class DecayStateMixer(Mixer):
+        """s_t = decay * s_{t-1} + x_t W_in^T ;  out_t = s_t W_out^T.  The state s lives in
+        the request's slot, so a sequence must be fed in order, each token once."""
+
+        def __init__(self, params, prefix, runtime):
+            super().__init__(params, prefix, runtime)
+            self.h, self.d, self.decay = params["hidden_size"], params["state_size"], params["decay"]
+
+        def tensor_specs(self):
+            return {self.prefix + "in.weight": TensorSpec((self.d, self.h)),
+                    self.prefix + "out.weight": TensorSpec((self.h, self.d))}
+
+        def bind(self, tensors):
+            self.w_in = tensors[self.prefix + "in.weight"].float()
+            self.w_out = tensors[self.prefix + "out.weight"].float()
+
+        def cache_need(self):
+            return FixedState((self.d,), tag="decay")
+
+        def forward(self, x, batch, cache, writes_cache=True):
+            u = x.float() @ self.w_in.t()
+            out = torch.empty((x.shape[0], self.h), dtype=torch.float32, device=x.device)
+            for start, n, slot in zip(batch.q_start, batch.q_len, batch.slot_ids):
+                s = cache.tensor[slot].clone()
+                for t in range(start, start + n):
+                    s = self.decay * s + u[t]
+                    out[t] = s @ self.w_out.t()
+                cache.tensor[slot] = s
+            return out.to(x.dtype)
+
+    class Top1Experts(FeedForward):
+        """Router logits in 32-bit, the best expert's ReLU MLP, weighted by its softmax probability."""
+
+        def __init__(self, params, prefix, runtime):
+            super().__init__(params, prefix, runtime)
+            self.h, self.i, self.e = params["hidden_size"], params["intermediate_size"], params["n_experts"]
+
+        def tensor_specs(self):
+            specs = {self.prefix + "router.weight": TensorSpec((self.e, self.h))}
+            for k in range(self.e):
+                specs[f"{self.prefix}experts.{k}.up.weight"] = TensorSpec((self.i, self.h))
+                specs[f"{self.prefix}experts.{k}.down.weight"] = TensorSpec((self.h, self.i))
+            return specs
+
+        def bind(self, tensors):
+            self.router = tensors[self.prefix + "router.weight"].float()
+            self.up = [tensors[f"{self.prefix}experts.{k}.up.weight"].float() for k in range(self.e)]
+            self.down = [tensors[f"{self.prefix}experts.{k}.down.weight"].float() for k in range(self.e)]
+
+        def forward(self, x, batch):
+            xf = x.float()
+            probs = torch.softmax(xf @ self.router.t(), dim=-1)
+            best = probs.argmax(dim=-1)
+            out = torch.zeros_like(xf)
+            for k in range(self.e):
+                rows = (best == k).nonzero().flatten()
+                if rows.numel():
+                    y = torch.relu(xf[rows] @ self.up[k].t()) @ self.down[k].t()
+                    out[rows] = y * probs[rows, k:k + 1]
+            return out.to(x.dtype)
+
+    register_mixer("toy_decay_state", DecayStateMixer, replace=True)
+    register_feed_forward("toy_top1_experts", Top1Experts, replace=True)
+
+    class ToyConfig(ModelConfig):
+        @classmethod
+        def from_json(cls, j):
+            return cls(architecture="ToyForCausalLM", raw=dict(j))
+
+    def norm(prefix):
+        return PartSpec("rmsnorm", {"size": H, "eps": EPS}, prefix=prefix)
+
+    def build(cfg):
+        rope = PartSpec("rope", {"head_dim": HD, "rotary_dim": HD, "theta": 10000.0, "scaling": None})
+        nope = PartSpec("none", {"head_dim": HD})
+
+        def attn(i, position, window):
+            return PartSpec("attention", {"hidden_size": H, "n_heads": NH, "n_kv_heads": NKV, "head_dim": HD,
+                                          "softmax_scale": HD ** -0.5, "window": window, "position": position},
+                            prefix=f"layers.{i}.attn.")
+
+        swiglu = lambda i: PartSpec("swiglu", {"hidden_size": H, "intermediate_size": INTER}, prefix=f"layers.{i}.mlp.")
+        layers = (
+            LayerSpec("prenorm", attn(0, rope, 0), norm("layers.0.n1."), swiglu(0), norm("layers.0.n2.")),
+            LayerSpec("prenorm", PartSpec("toy_decay_state", {"hidden_size": H, "state_size": D_STATE, "decay": DECAY},
+                                          prefix="layers.1.mix."), norm("layers.1.n1."),
+                      PartSpec("toy_top1_experts", {"hidden_size": H, "intermediate_size": INTER,
+                                                    "n_experts": N_EXPERTS}, prefix="layers.1.moe."),
+                      norm("layers.1.n2.")),
+            LayerSpec("prenorm", attn(2, nope, WINDOW), norm("layers.2.n1."), swiglu(2), norm("layers.2.n2.")),
+            LayerSpec("prenorm", attn(3, rope, 0), norm("layers.3.n1."), swiglu(3), norm("layers.3.n2.")),
+        )
+        # layer 0 runs twice (two caches of its own); the last run of layer 3 reads the cache
+        # that the first run of layer 0 wrote and writes none
+        schedule = (ScheduleItem(0), ScheduleItem(1), ScheduleItem(2), ScheduleItem(0), ScheduleItem(3, cache_of=0))
+        return ModelSpec(hidden_size=H, vocab_size=V,
+                         embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, prefix="embed."),
+                         layers=layers, schedule=schedule, final_norm=norm("final_norm."),
+                         head=PartSpec("linear_head", {"vocab_size": V, "hidden_size": H, "tied_to": "embed.weight",
+                                                       "require_own": False}, prefix="head."))
+
+    register_architecture("ToyForCausalLM", ToyConfig, build, replace=True)
+
+
+def toy_weights(seed=3):
+    rng = np.random.default_rng(seed)
+    r = lambda *s, std=0.08: bf16_round(rng.standard_normal(s).astype(np.float32) * std)
+    w = {"embed.weight": r(V, H, std=0.5), "final_norm.weight": bf16_round(1 + 0.1 * rng.standard_normal(H).astype(np.float32))}
+    for i in range(4):
+        for n in ("n1", "n2"):
+            w[f"layers.{i}.{n}.weight"] = bf16_round(1 + 0.1 * rng.standard_normal(H).astype(np.float32))
+    for i in (0, 2, 3):
+        w[f"layers.{i}.attn.q_proj.weight"] = r(NH * HD, H, std=0.3)
+        w[f"layers.{i}.attn.k_proj.weight"] = r(NKV * HD, H, std=0.3)
+        w[f"layers.{i}.attn.v_proj.weight"] = r(NKV * HD, H)
+        w[f"layers.{i}.attn.o_proj.weight"] = r(H, NH * HD)
+        w[f"layers.{i}.mlp.gate_proj.weight"] = r(INTER, H)
+        w[f"layers.{i}.mlp.up_proj.weight"] = r(INTER, H)
+        w[f"layers.{i}.mlp.down_proj.weight"] = r(H, INTER)
+    w["layers.1.mix.in.weight"] = r(D_STATE, H)
+    w["layers.1.mix.out.weight"] = r(H, D_STATE)
+    w["layers.1.moe.router.weight"] = r(N_EXPERTS, H, std=0.5)
+    for k in range(N_EXPERTS):
+        w[f"layers.1.moe.experts.{k}.up.weight"] = r(INTER, H)
+        w[f"layers.1.moe.experts.{k}.down.weight"] = r(H, INTER)
+    return w
+
+
+# ----------------------------------------------------------------------------- plain forward of the toy model
+
+def plain_forward(w, tokens):
+    w = {k: v.astype(np.float64) for k, v in w.items()}
+    T = len(tokens)
+    pos = np.arange(T)
+    freqs = np.power(np.float32(10000.0), np.arange(0, HD, 2, dtype=np.float32) / np.float32(HD))
+    h = P.embed(w["embed.weight"], tokens)
+    kept = {}
+
+    def attn_block(h, i, item, rope, window, kv_from=None):
+        p = f"layers.{i}."
+        xn = P.rms_norm(h, w[p + "n1.weight"], EPS)
+        q, k, v = P.project_qkv(xn, w[p + "attn.q_proj.weight"], w[p + "attn.k_proj.weight"],
+                                w[p + "attn.v_proj.weight"], NH, NKV, HD)
+        if rope:
+            q, k = P.apply_rope(q, pos, freqs), P.apply_rope(k, pos, freqs)
+        if kv_from is not None:
+            k, v = kept[kv_from]
+        kept[item] = (k, v)
+        h = h + P.attention(q, k, v, HD ** -0.5, window) @ w[p + "attn.o_proj.weight"].T
+        xn = P.rms_norm(h, w[p + "n2.weight"], EPS)
+        return h + P.swiglu_mlp(xn, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                w[p + "mlp.down_proj.weight"])
+
+    h = attn_block(h, 0, 0, True, 0)
+    # layer 1: decaying state, then top-1 experts
+    xn = P.rms_norm(h, w["layers.1.n1.weight"], EPS)
+    u = xn @ w["layers.1.mix.in.weight"].T
+    s = np.zeros(D_STATE)
+    mix = np.empty((T, H))
+    for t in range(T):
+        s = DECAY * s + u[t]
+        mix[t] = s @ w["layers.1.mix.out.weight"].T
+    h = h + mix
+    xn = P.rms_norm(h, w["layers.1.n2.weight"], EPS)
+    logits = xn @ w["layers.1.moe.router.weight"].T
+    probs = np.exp(logits - logits.max(-1, keepdims=True))
+    probs /= probs.sum(-1, keepdims=True)
+    moe = np.zeros((T, H))
+    for t in range(T):
+        k = int(np.argmax(probs[t]))
+        moe[t] = np.maximum(xn[t] @ w[f"layers.1.moe.experts.{k}.up.weight"].T, 0) @ \
+            w[f"layers.1.moe.experts.{k}.down.weight"].T * probs[t, k]
+    h = h + moe
+    h = attn_block(h, 2, 2, False, WINDOW)
+    h = attn_block(h, 0, 3, True, 0)
+    h = attn_block(h, 3, 4, True, 0, kv_from=0)
+    return P.rms_norm(h, w["final_norm.weight"], EPS) @ w["embed.weight"].T
+
+
+# ----------------------------------------------------------------------------- the test
+
+def test_toy_architecture_is_registered_built_and_stepped(tmp_path):
+    import torch
+    _register()
+    from mlxforge_b200.engine.replay import make_runner
+    from mlxforge_b200.engine.step import StepEntry
+    from mlxforge_b200.parts.base import FixedState, PagedKV
+    w = toy_weights()
+    d = write_model_dir(str(tmp_path / "toy"), {"architectures": ["ToyForCausalLM"]}, w, "bfloat16")
+    runner = make_runner(d, "float32", max_tokens=192)
+    layout = runner.model.cache_layout
+    # two paged groups (full attention: three lanes; windowed: one) and one state group
+    assert sorted((g.need.window, g.n_lanes) for g in layout.paged) == [(0, 2), (WINDOW, 1)]
+    assert [(type(g.need), g.n_lanes) for g in layout.state] == [(FixedState, 1)]
+    assert layout.item_lane[4] == layout.item_lane[0], "the last run reads the first run's lane"
+
+    rng = np.random.default_rng(0)
+    seqs = {"a": rng.integers(0, V, size=70).tolist(), "b": rng.integers(0, V, size=45).tolist()}
+    want = {k: plain_forward(w, t) for k, t in seqs.items()}
+    # a in portions of changing size with b's tokens beside it, one by one towards the end
+    live = {k: runner.cache.open_sequence() for k in seqs}
+    done = {k: 0 for k in seqs}
+    got = {k: {} for k in seqs}
+    sizes = {"a": [7, 2, 16, 5, 1, 1, 9, 2, 1, 1, 1, 3, 1, 20], "b": [1, 11, 2, 2, 1, 13, 1, 1, 1, 12]}
+    step = 0
+    while any(done[k] < len(seqs[k]) for k in seqs):
+        entries, keys = [], []
+        for k in seqs:
+            if done[k] >= len(seqs[k]) or (k == "b" and step % 3 == 2):
+                continue
+            n = min(sizes[k][(step) % len(sizes[k])], len(seqs[k]) - done[k])
+            entries.append(StepEntry(live[k], seqs[k][done[k]:done[k] + n], list(range(n))))
+            keys.append((k, done[k], n))
+            done[k] += n
+        step += 1
+        if not entries:
+            continue
+        logits = runner.step(entries).cpu().numpy()
+        row = 0
+        for k, start, n in keys:
+            for j in range(n):
+                got[k][start + j] = logits[row]
+                row += 1
+        runner.cache.check()
+    worst = max(float(np.max(np.abs(got[k][p] - want[k][p]))) for k in seqs for p in range(len(seqs[k])))
+    scale = max(float(np.max(np.abs(v))) for v in want.values())
+    assert worst <= 1e-4 * max(1.0, scale), worst
+    # the windowed group gave pages back as the window moved on; the full groups kept theirs
+    win = [g for g, gl in enumerate(layout.paged) if gl.need.window][0]
+    full = 1 - win
+    assert live["a"].pages_held(win) < live["a"].pages_held(full) == (70 + 15) // 16
+    for s in live.values():
+        runner.cache.close(s)
+    assert runner.cache.free_pages() == runner.cache.total_pages()
