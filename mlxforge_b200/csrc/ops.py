@@ -142,6 +142,47 @@ def skinny_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: b
                                      1 if swiglu else 0, _stream()), "skinny_linear")
 
 
+_STATUS = {}
+
+
+def kernel_status(device=None) -> torch.Tensor:
+    """The device word in which kernels with bounded waits record that a wait ran out."""
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _STATUS.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _STATUS[key] = t
+    return t
+
+
+def check_kernel_status() -> None:
+    """Raise if a kernel gave up a bounded wait since the last check (reads the word back)."""
+    for t in _STATUS.values():
+        code = int(t.item())
+        if code:
+            t.zero_()
+            raise KernelError(f"a kernel's bounded wait ran out (code {code}: 1 = copy producer, 2 = consumer)")
+
+
+def stream_max_rows() -> int:
+    return int(library().mf_stream_max_rows())
+
+
+def stream_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
+    """The few-row product with weights streamed by bulk copies (see gemv_stream.cu);
+    same operands and results as ``skinny_linear``, at most ``stream_max_rows()`` rows."""
+    _need_cuda(x, w, out)
+    M, K = x.shape
+    N = w.shape[0]
+    want = (M, N // 2) if swiglu else (M, N)
+    if w.shape[1] != K or tuple(out.shape) != want:
+        raise KernelError(f"stream_linear: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    check(library().mf_stream_linear(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out), M, N, K,
+                                     1 if swiglu else 0, kernel_status(x.device).data_ptr(), _stream()),
+          "stream_linear")
+
+
 def attention_decode_split(head_dim: int) -> int:
     """Keys per split of the decode kernel for a head size."""
     return int(library().mf_attention_decode_split(head_dim))

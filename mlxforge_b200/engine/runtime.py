@@ -31,6 +31,8 @@ class Runtime:
         # rows at or below which the bfloat16 product runs the skinny kernel
         self.skinny_max_rows = 16
         self.skinny_enabled = True
+        # rows at or below which the few-row product streams its weights by bulk copies
+        self.stream_max_rows = 16
 
     # ------------------------------------------------------------------ scratch
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -63,7 +65,7 @@ class Runtime:
         if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             raise ops.KernelError(f"linear: operand dtypes {x.dtype} x {w.dtype} are not a supported pair")
         if self._skinny(x, w):
-            ops.skinny_linear(x, w, out)
+            (ops.stream_linear if x.shape[0] <= self.stream_max_rows else ops.skinny_linear)(x, w, out)
             return out
         if out.dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)
@@ -79,7 +81,7 @@ class Runtime:
         up in groups of ``group``.  Few bfloat16 rows: one kernel with the product in
         its epilogue; otherwise the product, then the elementwise kernel."""
         if group == 8 and w_gu.shape[0] % 16 == 0 and self._skinny(x, w_gu):
-            ops.skinny_linear(x, w_gu, out, swiglu=True)
+            (ops.stream_linear if x.shape[0] <= self.stream_max_rows else ops.skinny_linear)(x, w_gu, out, swiglu=True)
             return out
         gu = self.linear(x, w_gu, self.buffer("ffn.gu", (x.shape[0], w_gu.shape[0])))
         ops.swiglu(gu, out, group)

@@ -310,6 +310,40 @@ def test_rope_kv_write(dtype, nh, nkv, hd, rot):
 # ----------------------------------------------------------------------------- few-row products
 
 @pytest.mark.parametrize("M,N,K", [(1, 304, 80), (8, 2048, 2048), (5, 307, 136), (16, 96, 200), (9, 1000, 64),
+                                   (3, 128256, 64), (8, 16, 8192), (2, 5000, 520), (7, 40, 1032), (16, 4737, 1536)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_stream_linear(M, N, K, out_dtype):
+    """The bulk-copy version: tiles that end inside a stage, K tails, more tiles than blocks."""
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(M * 1000 + N)
+    x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    w = bf16_round(rng.standard_normal((N, K)).astype(np.float32))
+    out = torch.full((M, N), float("nan"), dtype=torch_dtype(out_dtype), device="cuda")
+    ops.stream_linear(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out)
+    ops.check_kernel_status()
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    tol = 3e-6 * np.sqrt(K) * 4 if out_dtype == "float32" else 2.0 ** -8 * np.abs(want).max() + 1e-3
+    assert np.max(np.abs(host(out) - want)) < tol
+    if M > 1:
+        out1 = torch.empty((1, N), dtype=torch_dtype(out_dtype), device="cuda")
+        ops.stream_linear(dev(x[M - 1:M], torch.bfloat16), dev(w, torch.bfloat16), out1)
+        assert torch.equal(out1[0], out[M - 1])
+    # the swiglu epilogue, when the shape allows it
+    if N % 16 == 0 and out_dtype == "bfloat16":
+        I = N // 2
+        wg, wu = w[:I] * 0.2, w[I:] * 0.2
+        gu = bf16_round(np.stack([wg.reshape(I // 8, 8, K), wu.reshape(I // 8, 8, K)], axis=1).reshape(N, K))
+        act = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.stream_linear(dev(x, torch.bfloat16), dev(gu, torch.bfloat16), act, swiglu=True)
+        gg = x.astype(np.float64) @ bf16_round(wg).astype(np.float64).T
+        uu = x.astype(np.float64) @ bf16_round(wu).astype(np.float64).T
+        want = gg / (1 + np.exp(-gg)) * uu
+        assert np.all(np.abs(host(act) - want) <= 2.0 ** -7 * (np.abs(want) + 1e-2))
+    ops.check_kernel_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 304, 80), (8, 2048, 2048), (5, 307, 136), (16, 96, 200), (9, 1000, 64),
                                    (32, 48, 72), (3, 128256, 64), (8, 16, 8192)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
 def test_skinny_linear(M, N, K, out_dtype):
