@@ -183,6 +183,29 @@ def stream_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: b
           "stream_linear")
 
 
+def gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 product takes these operands (TMA needs 16-byte row strides)."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
+    """out = x @ w^T on the tcgen05 tensor cores (bfloat16 operands; out bfloat16 or float32);
+    with ``swiglu`` the rows of w interleave gate and up in groups of 8 and out is
+    [M, N/2] = silu(gate) * up."""
+    _need_cuda(x, w, out)
+    M, K = x.shape
+    N = w.shape[0]
+    want = (M, N // 2) if swiglu else (M, N)
+    if w.shape[1] != K or tuple(out.shape) != want:
+        raise KernelError(f"gemm_bf16: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if swiglu and out.dtype != torch.bfloat16:
+        raise KernelError("gemm_bf16: the gated epilogue writes bfloat16")
+    epi = 2 if swiglu else (1 if out.dtype == torch.float32 else 0)
+    check(library().mf_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, epi,
+                                 kernel_status(x.device).data_ptr(), _stream()), "gemm_bf16")
+
+
 def attention_decode_split(head_dim: int) -> int:
     """Keys per split of the decode kernel for a head size."""
     return int(library().mf_attention_decode_split(head_dim))

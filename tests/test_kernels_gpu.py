@@ -429,3 +429,47 @@ def test_attention_prefill(case):
             want = pc.reference(q[starts[s] + j], s, pos, scale, window)
             d = np.max(np.abs(got[starts[s] + j] - want))
             assert d < 1.5e-2, (s, j, pos, d)
+
+
+# ----------------------------------------------------------------------------- tcgen05 product
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (2048, 3072, 2048), (300, 520, 136), (17, 96, 80),
+                                   (129, 257, 72), (1000, 128, 4096), (64, 16384, 512)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_gemm_tcgen05(M, N, K, out_dtype):
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(M + N + K)
+    x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    w = bf16_round(rng.standard_normal((N, K)).astype(np.float32))
+    out = torch.full((M, N), float("nan"), dtype=torch_dtype(out_dtype), device="cuda")
+    ops.gemm_bf16(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out)
+    ops.check_kernel_status()
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    got = host(out)
+    assert np.isfinite(got).all()
+    # Forward error bound of a float32 sum: each of the K additions may lose 2^-23 (the
+    # tensor cores truncate) of the running magnitude, which sum(|x||w|) bounds.  A wrong
+    # tile, a dropped k-step or a 16-bit accumulator would be orders of magnitude beyond it.
+    bound = 2.0 ** -19 * (np.abs(x).astype(np.float64) @ np.abs(w).astype(np.float64).T) + 1e-6
+    if out_dtype == "bfloat16":
+        bound = bound + 2.0 ** -8 * np.abs(want)
+    assert np.all(np.abs(got - want) <= bound), float(np.max(np.abs(got - want) / bound))
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (2048, 8192, 2048), (77, 136, 80)])
+def test_gemm_tcgen05_swiglu(M, I, K):
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(I)
+    x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    wg = bf16_round(rng.standard_normal((I, K)).astype(np.float32) * 0.1)
+    wu = bf16_round(rng.standard_normal((I, K)).astype(np.float32) * 0.1)
+    gu = np.stack([wg.reshape(I // 8, 8, K), wu.reshape(I // 8, 8, K)], axis=1).reshape(2 * I, K)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_bf16(dev(x, torch.bfloat16), dev(gu, torch.bfloat16), out, swiglu=True)
+    ops.check_kernel_status()
+    g = x.astype(np.float64) @ wg.astype(np.float64).T
+    u = x.astype(np.float64) @ wu.astype(np.float64).T
+    want = g / (1 + np.exp(-g)) * u
+    assert np.all(np.abs(host(out) - want) <= 2.0 ** -7 * (np.abs(want) + 1e-2))
