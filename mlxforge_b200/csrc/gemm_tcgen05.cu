@@ -1,7 +1,7 @@
 // C[M, N] = A[M, K] * W[N, K]^T for many rows (prompt portions): bfloat16 operands, float32
 // accumulation in tensor memory, on the 5th-generation tensor cores.
 //
-// One block computes a 128 x BN tile of C (BN = 256 or 128):
+// A block computes 128 x BN tiles of C (BN = 256 or 128), one after the other:
 //   warp 0     one thread issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of a
 //              128 x 64 tile of A and a BN x 64 tile of W into a ring of STAGES buffers, each
 //              signalled by an mbarrier with the byte count;
@@ -95,22 +95,77 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
+// Stores 32 consecutive columns of one row of the accumulator.
+template <int EPI>
+__device__ __forceinline__ void store_chunk(void* __restrict__ C, const unsigned (&r)[32], int row, int col, int N) {
+  if (EPI == 0) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (long long)row * N + col;
+    if (col + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+      for (int v = 0; v < 4; v++) {
+        uint4 pk;
+        pk.x = pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+        pk.y = pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+        pk.z = pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+        pk.w = pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+        reinterpret_cast<uint4*>(dst)[v] = pk;
+      }
+    } else {
+      for (int j = 0; j < 32 && col + j < N; j++) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+    }
+  } else if (EPI == 1) {
+    float* dst = reinterpret_cast<float*>(C) + (long long)row * N + col;
+    if (col + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+      for (int v = 0; v < 8; v++)
+        reinterpret_cast<float4*>(dst)[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                        __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+    } else {
+      for (int j = 0; j < 32 && col + j < N; j++) dst[j] = __uint_as_float(r[j]);
+    }
+  } else {
+    // 32 columns = two groups of [8 gate | 8 up] -> 16 outputs at column col / 2
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (long long)row * (N / 2) + col / 2;
+#pragma unroll
+    for (int grp = 0; grp < 2; grp++) {
+      if (col + grp * 16 + 16 > N) break;
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        o[j] = silu_mul(__uint_as_float(r[grp * 16 + j]), __uint_as_float(r[grp * 16 + 8 + j]));
+      if ((((uintptr_t)(dst + grp * 8)) & 15) == 0) {
+        uint4 pk;
+        pk.x = pack_bf16(o[0], o[1]); pk.y = pack_bf16(o[2], o[3]);
+        pk.z = pack_bf16(o[4], o[5]); pk.w = pack_bf16(o[6], o[7]);
+        *reinterpret_cast<uint4*>(dst + grp * 8) = pk;
+      } else {
+        for (int j = 0; j < 8; j++) dst[grp * 8 + j] = __float2bfloat16_rn(o[j]);
+      }
+    }
+  }
+}
+
 // EPI 0: C bfloat16 [M, N].  EPI 1: C float32 [M, N].  EPI 2: C bfloat16 [M, N/2] = silu(gate) * up.
+// Persistent: a block walks tiles (tile, tile + grid, ...; the M index runs fastest, so blocks
+// that run together share tiles of W).  Two accumulators in tensor memory alternate, so the
+// epilogue of one tile runs while the products of the next are issued.
 template <int BN, int EPI>
 __global__ void __launch_bounds__(192)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ C,
             int M, int N, int K, int* __restrict__ status) {
   constexpr int B_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = 2 * BN;
   extern __shared__ unsigned char raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 1);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 4);
   const unsigned smem_u = smem_u32(smem), bars_u = smem_u32(bars);
-  const unsigned full0 = bars_u, empty0 = bars_u + 8 * STAGES, acc_bar = bars_u + 16 * STAGES;
+  const unsigned full0 = bars_u, empty0 = bars_u + 8 * STAGES;
+  const unsigned acc_full0 = bars_u + 16 * STAGES, acc_empty0 = acc_full0 + 16;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int n_mt = (M + BM - 1) / BM, n_nt = (N + BN - 1) / BN, n_tiles = n_mt * n_nt;
   const int n_kt = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -118,11 +173,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int a = 0; a < 2; a++) {
+      mbar_init(acc_full0 + 8 * a, 1);       // the issuer's commit
+      mbar_init(acc_empty0 + 8 * a, 4);      // one arrive per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(BN));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -133,13 +191,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      for (int kt = 0; kt < n_kt; kt++) {
-        const int s = kt % STAGES, round = kt / STAGES;
-        if (round > 0) mbar_wait(empty0 + 8 * s, (round - 1) & 1, status, 11);
-        const unsigned full = full0 + 8 * s;
-        mbar_expect_tx(full, STAGE_BYTES);
-        tma_load_2d(smem_u + s * STAGE_BYTES, &map_a, kt * BK, m0, full);
-        tma_load_2d(smem_u + s * STAGE_BYTES + A_BYTES, &map_w, kt * BK, n0, full);
+      unsigned it = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int m0 = (tile % n_mt) * BM, n0 = (tile / n_mt) * BN;
+        for (int kt = 0; kt < n_kt; kt++, it++) {
+          const unsigned s = it % STAGES, round = it / STAGES;
+          if (round > 0) mbar_wait(empty0 + 8 * s, (round - 1) & 1, status, 11);
+          const unsigned full = full0 + 8 * s;
+          mbar_expect_tx(full, STAGE_BYTES);
+          tma_load_2d(smem_u + s * STAGE_BYTES, &map_a, kt * BK, m0, full);
+          tma_load_2d(smem_u + s * STAGE_BYTES + A_BYTES, &map_w, kt * BK, n0, full);
+        }
       }
     }
   } else if (warp == 1) {
@@ -147,82 +209,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (lane == 0) {
       // instruction descriptor: D float32, A and B bfloat16, both K-major, N, M
       const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
-      for (int kt = 0; kt < n_kt; kt++) {
-        const int s = kt % STAGES, round = kt / STAGES;
-        mbar_wait(full0 + 8 * s, round & 1, status, 12);
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const unsigned a_addr = smem_u + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
+      unsigned it = 0, i = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, i++) {
+        const unsigned acc = i & 1, use = i >> 1;
+        if (use > 0) {
+          mbar_wait(acc_empty0 + 8 * acc, (use - 1) & 1, status, 14);     // the epilogue has drained it
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        }
+        const unsigned tmem_c = tmem_base + acc * BN;
+        for (int kt = 0; kt < n_kt; kt++, it++) {
+          const unsigned s = it % STAGES, round = it / STAGES;
+          mbar_wait(full0 + 8 * s, round & 1, status, 12);
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const unsigned a_addr = smem_u + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
 #pragma unroll
-        for (int k4 = 0; k4 < BK / 16; k4++)
-          umma(tmem_base, smem_desc(a_addr + k4 * 32), smem_desc(b_addr + k4 * 32), idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
-        umma_commit(empty0 + 8 * s);          // the stage is free once these products have read it
+          for (int k4 = 0; k4 < BK / 16; k4++)
+            umma(tmem_c, smem_desc(a_addr + k4 * 32), smem_desc(b_addr + k4 * 32), idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
+          umma_commit(empty0 + 8 * s);          // the stage is free once these products have read it
+        }
+        umma_commit(acc_full0 + 8 * acc);        // this tile's accumulator is complete
       }
-      umma_commit(acc_bar);                    // the accumulator is complete
     }
   } else {
     // ------------------------------------------------------------ epilogue (4 warps, 32 rows each)
     const int lg = warp & 3;                   // the 32 lanes of tensor memory this warp may read
-    const int row = m0 + lg * 32 + lane;
-    mbar_wait(acc_bar, 0, status, 13);
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    unsigned i = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, i++) {
+      const int m0 = (tile % n_mt) * BM, n0 = (tile / n_mt) * BN;
+      const unsigned acc = i & 1, use = i >> 1;
+      const int row = m0 + lg * 32 + lane;
+      mbar_wait(acc_full0 + 8 * acc, use & 1, status, 13);
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; c++) {
-      unsigned r[32];
-      tmem_ld32(tmem_base + ((unsigned)(lg * 32) << 16) + (unsigned)(c * 32), r);
-      const int col = n0 + c * 32;
-      if (row >= M || col >= N) continue;
-      if (EPI == 0) {
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (long long)row * N + col;
-        if (col + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
-#pragma unroll
-          for (int v = 0; v < 4; v++) {
-            uint4 pk;
-            pk.x = pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-            pk.y = pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-            pk.z = pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-            pk.w = pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-            reinterpret_cast<uint4*>(dst)[v] = pk;
-          }
-        } else {
-          for (int j = 0; j < 32 && col + j < N; j++) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-        }
-      } else if (EPI == 1) {
-        float* dst = reinterpret_cast<float*>(C) + (long long)row * N + col;
-        if (col + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
-#pragma unroll
-          for (int v = 0; v < 8; v++)
-            reinterpret_cast<float4*>(dst)[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                                            __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-        } else {
-          for (int j = 0; j < 32 && col + j < N; j++) dst[j] = __uint_as_float(r[j]);
-        }
-      } else {
-        // 32 columns = two groups of [8 gate | 8 up] -> 16 outputs at column col / 2
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (long long)row * (N / 2) + col / 2;
-#pragma unroll
-        for (int grp = 0; grp < 2; grp++) {
-          if (col + grp * 16 + 16 > N) break;
-          float o[8];
-#pragma unroll
-          for (int j = 0; j < 8; j++)
-            o[j] = silu_mul(__uint_as_float(r[grp * 16 + j]), __uint_as_float(r[grp * 16 + 8 + j]));
-          if ((((uintptr_t)(dst + grp * 8)) & 15) == 0) {
-            uint4 pk;
-            pk.x = pack_bf16(o[0], o[1]); pk.y = pack_bf16(o[2], o[3]);
-            pk.z = pack_bf16(o[4], o[5]); pk.w = pack_bf16(o[6], o[7]);
-            *reinterpret_cast<uint4*>(dst + grp * 8) = pk;
-          } else {
-            for (int j = 0; j < 8; j++) dst[grp * 8 + j] = __float2bfloat16_rn(o[j]);
-          }
-        }
+      for (int c = 0; c < BN / 32; c++) {
+        unsigned r[32];
+        tmem_ld32(tmem_base + ((unsigned)(lg * 32) << 16) + acc * BN + (unsigned)(c * 32), r);
+        const int col = n0 + c * 32;
+        if (row < M && col < N) store_chunk<EPI>(C, r, row, col, N);
       }
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(acc_empty0 + 8 * acc) : "memory");
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(BN));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
   }
 }
 
@@ -290,15 +324,22 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int* stat
   if (rc) return rc;
   rc = tensor_map(W, N, K, BN, &mw);
   if (rc) return rc;
-  const size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + 2 * STAGES * 8 + 8 + 16 + 1024;
+  const size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
-  gemm_kernel<BN, EPI><<<grid, 192, smem, stream>>>(ma, mw, C, M, N, K, status);
+  static int n_sms = 0;
+  if (n_sms == 0) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  gemm_kernel<BN, EPI><<<n_tiles < n_sms ? n_tiles : n_sms, 192, smem, stream>>>(ma, mw, C, M, N, K, status);
   return (int)cudaGetLastError();
 }
 

@@ -53,6 +53,7 @@ class EngineConfig:
     prefill_chunk: int = 512
     skinny_mm: bool = True             # few-row products by the skinny kernel
     cuda_graphs: bool = True           # replay decode-only steps from captured graphs
+    gemm: str = ""                     # many-row products: "library" | "tcgen05" ("" = MLXFORGE_GEMM or library)
     rope_scaling: str = ""             # JSON object replacing the checkpoint's rope_scaling
 
     def validate(self) -> None:
@@ -83,6 +84,10 @@ class Engine:
         rt = self.model.rt
         rt.skinny_enabled = bool(config.skinny_mm)
         rt.reserve_rows = config.token_budget
+        if config.gemm:
+            if config.gemm not in ("library", "tcgen05"):
+                raise ValueError(f"EngineConfig: gemm must be 'library' or 'tcgen05', got '{config.gemm}'")
+            rt.gemm_backend = config.gemm
         elt = 4 if dtype == torch.float32 else 2
         per_token = max(1, self.model.cache_layout.bytes_per_token(elt))
         tokens = config.kv_pool_tokens if config.kv_pool_tokens > 0 else config.kv_pool_bytes // per_token

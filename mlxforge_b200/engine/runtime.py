@@ -5,6 +5,7 @@ how many rows there are).
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -33,6 +34,11 @@ class Runtime:
         self.skinny_enabled = True
         # rows at or below which the few-row product streams its weights by bulk copies
         self.stream_max_rows = 16
+        # many-row bfloat16 products: "library" (cuBLAS through torch.mm, as the reference uses
+        # its library's matmul there) or "tcgen05" (this engine's own tensor-memory kernel)
+        self.gemm_backend = os.environ.get("MLXFORGE_GEMM", "library")
+        if self.gemm_backend not in ("library", "tcgen05"):
+            raise ValueError(f"MLXFORGE_GEMM must be 'library' or 'tcgen05', got '{self.gemm_backend}'")
 
     # ------------------------------------------------------------------ scratch
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -67,6 +73,9 @@ class Runtime:
         if self._skinny(x, w):
             (ops.stream_linear if x.shape[0] <= self.stream_max_rows else ops.skinny_linear)(x, w, out)
             return out
+        if self.gemm_backend == "tcgen05" and ops.gemm_ok(x, w):
+            ops.gemm_bf16(x, w, out)
+            return out
         if out.dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)
         else:
@@ -82,6 +91,9 @@ class Runtime:
         its epilogue; otherwise the product, then the elementwise kernel."""
         if group == 8 and w_gu.shape[0] % 16 == 0 and self._skinny(x, w_gu):
             (ops.stream_linear if x.shape[0] <= self.stream_max_rows else ops.skinny_linear)(x, w_gu, out, swiglu=True)
+            return out
+        if self.gemm_backend == "tcgen05" and group == 8 and w_gu.shape[0] % 16 == 0 and ops.gemm_ok(x, w_gu):
+            ops.gemm_bf16(x, w_gu, out, swiglu=True)
             return out
         gu = self.linear(x, w_gu, self.buffer("ffn.gu", (x.shape[0], w_gu.shape[0])))
         ops.swiglu(gu, out, group)

@@ -97,3 +97,19 @@ def test_mixed_reuses_pages(models, tmp_path):
     got = TT.read_outputs(trace, out_dir, cfg["vocab_size"])
     d_max, where = TT.worst(got, expected)
     assert d_max <= tols["float32"], (d_max, where)
+
+
+@pytest.mark.parametrize("mode", ["whole", "portions", "mixed"])
+def test_replay_with_the_tcgen05_products(models, tmp_path, mode, monkeypatch):
+    """The same traces with this engine's own tensor-memory product kernel in place of the
+    library's for the many-row products."""
+    monkeypatch.setenv("MLXFORGE_GEMM", "tcgen05")
+    from mlxforge_b200.csrc import ops
+    for which in ("B", "C"):
+        d, cfg, reqs, expected, tols = models[(which, 12.0)]
+        trace = MODES[mode](reqs)
+        out_dir = _replay(d, "bfloat16", trace, tmp_path / which)
+        ops.check_kernel_status()
+        got = TT.read_outputs(trace, out_dir, cfg["vocab_size"])
+        d_max, where = TT.worst(got, expected)
+        assert d_max <= tols["bfloat16"], (which, mode, d_max, where)
