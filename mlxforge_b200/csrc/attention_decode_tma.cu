@@ -1,0 +1,399 @@
+// Decode attention for head size 64 with the keys and values brought in by the TMA unit.
+//
+// It computes exactly what attn_decode_kernel (attention_decode.cu) computes and writes the
+// same per-split partial results (same split size, same merge kernel after it), but is built
+// around the memory system instead of around the warps:
+//   * one persistent block per SM walks work items (token, KV head x head group, split of 512
+//     keys), item = block, block + grid, ...;
+//   * a producer warp issues one 2-D tensor copy per granule of 16 keys (a page holds whole
+//     granules, so a granule is 16 contiguous rows of the pool): 8 key boxes and 8 value boxes
+//     per stage of 128 keys, 128-byte swizzled, into a ring of STAGES stages, each signalled by
+//     an mbarrier; it runs ahead across item boundaries, so about 130 KB per SM are always on
+//     their way, and no thread computes an address per 16 bytes;
+//   * eight consumer warps take 16 keys of a stage each (scores and the second product on
+//     mma.sync as in the other kernel, softmax statistics in fp32, running over the item's
+//     stages), hand the stage back, and at the end of an item combine into one partial result.
+// Query rows of an item are one contiguous run of G * 64 values: one bulk copy.
+//
+// All waits are bounded (see gemv_stream.cu).  Formula: src/model/sdpa.cpp:71-95.
+#include "common.cuh"
+#include "tma_host.cuh"
+
+namespace {
+
+constexpr int CW = 8;                   // consumer warps
+constexpr int HD = 64;
+constexpr int TILE = 128;               // keys per stage: 8 granules of 16
+constexpr int GRAN_BYTES = 16 * HD * 2; // 2 KB: 16 rows of 128 bytes
+constexpr int STAGE_BYTES = 2 * 8 * GRAN_BYTES;   // keys then values: 32 KB
+constexpr int STAGES = 5;
+constexpr int SPLIT_KEYS = 512;
+constexpr int Q_BYTES = 16 * HD * 2;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr unsigned WAIT_LIMIT = 1u << 24;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* status, int code) {
+  for (unsigned i = 0; i < WAIT_LIMIT; i++) {
+    unsigned done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  if (status) atomicExch(status, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_copy(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CW * 32) : "memory"); }
+
+// What an item is, computed the same way by the producer and the consumers.
+struct Item {
+  int t, kvh, head0, n_rows, split, pos, lo, seq, tile0, tile1;
+  bool live;
+};
+__device__ __forceinline__ Item make_item(int item, int max_splits, int groups, int hgroups, int G,
+                                          const int* positions, const int* seq_of_token, int window) {
+  Item it;
+  it.split = item % max_splits;
+  const int rest = item / max_splits;
+  const int grp = rest % groups;
+  it.t = rest / groups;
+  it.kvh = grp / hgroups;
+  const int hg = grp - it.kvh * hgroups;
+  it.head0 = it.kvh * G + hg * 16;
+  it.n_rows = min(16, G - hg * 16);
+  it.pos = positions[it.t];
+  it.seq = seq_of_token[it.t];
+  it.lo = (window > 0 && it.pos - window + 1 > 0) ? it.pos - window + 1 : 0;
+  const int k_begin = it.split * SPLIT_KEYS;
+  it.live = !(k_begin > it.pos || k_begin + SPLIT_KEYS <= it.lo);
+  it.tile0 = max(k_begin, it.lo) / TILE;
+  it.tile1 = min(k_begin + SPLIT_KEYS - 1, it.pos) / TILE;
+  return it;
+}
+
+__global__ void __launch_bounds__((CW + 1) * 32)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const __nv_bfloat16* __restrict__ q, float* __restrict__ part_o, float* __restrict__ part_ml,
+                       const int* __restrict__ positions, const int* __restrict__ seq_of_token, PagedView pv,
+                       int n_heads, int n_tokens, float scale_log2, int window, int max_splits,
+                       int* __restrict__ status) {
+  extern __shared__ unsigned char raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* ring = smem;                                             // [STAGES][K 8 x 2 KB | V 8 x 2 KB]
+  unsigned char* q_s = smem + STAGES * STAGE_BYTES;                       // [2][16][64] bf16
+  float* comb = reinterpret_cast<float*>(q_s + 2 * Q_BYTES);              // [CW][16][HD + 2]: m, l, o[HD]
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(comb + CW * 16 * (HD + 2));
+  const unsigned ring_u = smem_u32(ring), q_u = smem_u32(q_s), bars_u = smem_u32(bars);
+  const unsigned full0 = bars_u, empty0 = bars_u + 8 * STAGES;
+  const unsigned qfull0 = bars_u + 16 * STAGES, qempty0 = qfull0 + 16;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = n_heads / pv.n_kv_heads, hgroups = (G + 15) / 16, groups = pv.n_kv_heads * hgroups;
+  const int n_items = n_tokens * groups * max_splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, CW);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(qfull0 + 8 * b, 1);
+      mbar_init(qempty0 + 8 * b, CW);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  // rows of q beyond the group stay zero for the whole kernel
+  for (int i = threadIdx.x; i < 2 * Q_BYTES / 16; i += blockDim.x) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");    // before the copy unit writes there
+  __syncthreads();
+  pdl_wait();                       // q and the newest keys and values come from the kernel before
+  if (threadIdx.x == 0) pdl_launch();
+
+  if (warp == CW) {
+    // ------------------------------------------------------------ producer warp
+    // What the copies of an item need from memory (the token's position and sequence, and the
+    // page of each of the split's 32 granules: lane l looks up granule l) is fetched one item
+    // ahead, so that the ring never waits for a table lookup.
+    auto fetch = [&](int item, Item& w, int& row) {
+      w = make_item(item, max_splits, groups, hgroups, G, positions, seq_of_token, window);
+      const int key16 = w.split * SPLIT_KEYS + lane * 16;
+      row = -1;
+      if (w.live && key16 <= w.pos && key16 + 16 > w.lo) {
+        const int blk = key16 / pv.page_size;
+        const int page = pv.block_table[(long long)w.seq * pv.bt_stride + blk];
+        row = (page * pv.n_kv_heads + w.kvh) * pv.page_size + (key16 - blk * pv.page_size);
+      }
+    };
+    unsigned it = 0, live_items = 0;
+    int item = blockIdx.x;
+    Item w, w_next;
+    int row = -1, row_next = -1;
+    w_next.live = false;
+    if (item < n_items) fetch(item, w, row);
+    while (item < n_items) {
+      const int next = item + gridDim.x;
+      if (next < n_items) fetch(next, w_next, row_next);
+      if (w.live) {
+        // the item's queries: G contiguous rows
+        if (lane == 0) {
+          const unsigned b = live_items & 1, use = live_items >> 1;
+          if (use > 0) mbar_wait(qempty0 + 8 * b, (use - 1) & 1, status, 21);
+          mbar_expect_tx(qfull0 + 8 * b, (unsigned)w.n_rows * HD * 2);
+          bulk_copy(q_u + b * Q_BYTES, q + ((long long)w.t * n_heads + w.head0) * HD, (unsigned)w.n_rows * HD * 2,
+                    qfull0 + 8 * b);
+        }
+        live_items++;
+        for (int tile = w.tile0; tile <= w.tile1; tile++, it++) {
+          const unsigned s = it % STAGES, round = it / STAGES;
+          // lanes 0..7: the key box of granule `lane`; lanes 8..15: its value box
+          const int gran = lane & 7;
+          const int src_lane = (tile * TILE - w.split * SPLIT_KEYS) / 16 + gran;     // who looked this granule up
+          const int box_row = __shfl_sync(0xffffffffu, row, src_lane);
+          const bool valid = lane < 16 && box_row >= 0;
+          const unsigned n_valid = __popc(__ballot_sync(0xffffffffu, valid));
+          if (lane == 0) {
+            if (round > 0) mbar_wait(empty0 + 8 * s, (round - 1) & 1, status, 22);
+            mbar_expect_tx(full0 + 8 * s, n_valid * GRAN_BYTES);
+          }
+          __syncwarp();
+          if (valid) {
+            const unsigned dst = ring_u + s * STAGE_BYTES + (lane >> 3) * 8 * GRAN_BYTES + gran * GRAN_BYTES;
+            tma_load_2d(dst, lane < 8 ? &map_k : &map_v, 0, box_row, full0 + 8 * s);
+          }
+        }
+      }
+      w = w_next;
+      row = row_next;
+      item = next;
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int g = lane >> 2, tq = lane & 3;
+  unsigned it = 0, live_items = 0;
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const Item w = make_item(item, max_splits, groups, hgroups, G, positions, seq_of_token, window);
+    if (!w.live) continue;
+    // ---- the query tile as A fragments (read once per item)
+    unsigned qa[HD / 16][4];
+    {
+      const unsigned b = live_items & 1, use = live_items >> 1;
+      mbar_wait(qfull0 + 8 * b, use & 1, status, 23);
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; kk++)
+        ldmatrix_x4(qa[kk], q_u + b * Q_BYTES + (lane & 15) * (HD * 2) + (kk * 16 + (lane >> 4) * 8) * 2);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(qempty0 + 8 * b);
+    }
+    live_items++;
+    float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; d++) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+    for (int tile = w.tile0; tile <= w.tile1; tile++, it++) {
+      const unsigned s = it % STAGES, round = it / STAGES;
+      mbar_wait(full0 + 8 * s, round & 1, status, 24);
+      const int w_begin = tile * TILE + warp * 16;                 // this warp's granule
+      if (w_begin <= w.pos && w_begin + 16 > w.lo) {
+        const unsigned k_box = ring_u + s * STAGE_BYTES + warp * GRAN_BYTES;
+        const unsigned v_box = k_box + 8 * GRAN_BYTES;
+        // ---- scores S[16 heads x 16 keys]; rows of a box are 128 bytes, 16-byte pieces swizzled by row & 7
+        float sc[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; j++) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+        const int mi = lane >> 3, r8 = lane & 7;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; kk++) {
+          unsigned b[4];
+          const int key = (mi >> 1) * 8 + r8, piece = kk * 2 + (mi & 1);
+          ldmatrix_x4(b, k_box + key * 128 + ((piece ^ (key & 7)) << 4));
+          mma_bf16(sc[0], qa[kk], b[0], b[1]);
+          mma_bf16(sc[1], qa[kk], b[2], b[3]);
+        }
+        const bool edge = w_begin < w.lo || w_begin + 15 > w.pos;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            float v = sc[j][e] * scale_log2;
+            if (edge) {
+              const int key = w_begin + j * 8 + tq * 2 + (e & 1);
+              if (key < w.lo || key > w.pos) v = -INFINITY;
+            }
+            sc[j][e] = v;
+            mx[e >> 1] = fmaxf(mx[e >> 1], v);
+          }
+        }
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+          const float m_new = fmaxf(m_row[h], mx[h]);
+          m_use[h] = (m_new == -INFINITY) ? 0.f : m_new;
+          alpha[h] = (m_row[h] == -INFINITY) ? 0.f : exp2f(m_row[h] - m_use[h]);
+          m_row[h] = m_new;
+        }
+        float sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const float p = exp2f(sc[j][e] - m_use[e >> 1]);
+            sc[j][e] = p;
+            sum[e >> 1] += p;
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
+          sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
+          l_row[h] = l_row[h] * alpha[h] + sum[h];
+        }
+#pragma unroll
+        for (int d = 0; d < HD / 8; d++) {
+          o[d][0] *= alpha[0]; o[d][1] *= alpha[0];
+          o[d][2] *= alpha[1]; o[d][3] *= alpha[1];
+        }
+        if (edge) {
+          // rows of the box beyond the visible range hold whatever the page held before: their
+          // probability is exactly 0, but 0 x NaN would still poison the product, so clear them
+          for (int r = 0; r < 16; r++) {
+            const int key = w_begin + r;
+            if ((key < w.lo || key > w.pos) && lane < 8)
+              asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(v_box + r * 128 + lane * 16), "r"(0u) : "memory");
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+          __syncwarp();
+        }
+        // ---- O[16 x 64] += P V
+        unsigned a[4];
+        a[0] = pack_bf16(sc[0][0], sc[0][1]);
+        a[1] = pack_bf16(sc[0][2], sc[0][3]);
+        a[2] = pack_bf16(sc[1][0], sc[1][1]);
+        a[3] = pack_bf16(sc[1][2], sc[1][3]);
+#pragma unroll
+        for (int d = 0; d < HD / 8; d += 2) {
+          unsigned b[4];
+          const int key = (mi & 1) * 8 + r8, piece = d + (mi >> 1);
+          ldmatrix_x4_trans(b, v_box + key * 128 + ((piece ^ (key & 7)) << 4));
+          mma_bf16(o[d], a, b[0], b[1]);
+          mma_bf16(o[d + 1], a, b[2], b[3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    }
+
+    // ---- combine the 8 warps into the item's partial result (rows of the group only)
+    constexpr int CS = HD + 2;
+    if (tq == 0) {
+      if (g < w.n_rows) { comb[(warp * 16 + g) * CS] = m_row[0]; comb[(warp * 16 + g) * CS + 1] = l_row[0]; }
+      if (g + 8 < w.n_rows) { comb[(warp * 16 + g + 8) * CS] = m_row[1]; comb[(warp * 16 + g + 8) * CS + 1] = l_row[1]; }
+    }
+#pragma unroll
+    for (int d = 0; d < HD / 8; d++) {
+      if (g < w.n_rows) *reinterpret_cast<float2*>(comb + (warp * 16 + g) * CS + 2 + d * 8 + tq * 2) = make_float2(o[d][0], o[d][1]);
+      if (g + 8 < w.n_rows)
+        *reinterpret_cast<float2*>(comb + (warp * 16 + g + 8) * CS + 2 + d * 8 + tq * 2) = make_float2(o[d][2], o[d][3]);
+    }
+    consumer_sync();
+    for (int i = threadIdx.x; i < w.n_rows * HD; i += CW * 32) {
+      const int r = i / HD, d = i - r * HD;
+      float M = -INFINITY;
+#pragma unroll
+      for (int cw = 0; cw < CW; cw++) M = fmaxf(M, comb[(cw * 16 + r) * CS]);
+      float L = 0.f, acc = 0.f;
+#pragma unroll
+      for (int cw = 0; cw < CW; cw++) {
+        const float mw = comb[(cw * 16 + r) * CS];
+        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        L += comb[(cw * 16 + r) * CS + 1] * f;
+        acc += comb[(cw * 16 + r) * CS + 2 + d] * f;
+      }
+      const long long row = ((long long)w.t * n_heads + w.head0 + r) * max_splits + w.split;
+      part_o[row * HD + d] = acc;
+      if (d == 0) {
+        part_ml[row * 2 + 0] = M;
+        part_ml[row * 2 + 1] = L;
+      }
+    }
+    consumer_sync();       // `comb` is free for the next item
+  }
+}
+
+}  // namespace
+
+// Launches the first kernel of the decode attention for head size 64 (the merge kernel of
+// attention_decode.cu follows it).  Returns MF_ERR_BAD_ARG when this path does not apply.
+int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
+                      float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv, long long pool_rows,
+                      const int* positions, const int* seq_of_token, float scale, int window, int max_ctx,
+                      int* status, cudaStream_t stream) {
+  if (pv.head_dim != HD || pv.page_size % 16) return MF_ERR_BAD_ARG;
+  CUtensorMap mk, mv;
+  int rc = tma_host::bf16_map(k_pool, pool_rows, HD, 16, HD, &mk);
+  if (rc) return rc;
+  rc = tma_host::bf16_map(v_pool, pool_rows, HD, 16, HD, &mv);
+  if (rc) return rc;
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 2 * Q_BYTES + (size_t)CW * 16 * (HD + 2) * 4 + (2 * STAGES + 4) * 8 + 1024;
+  static bool configured = false;
+  static int n_sms = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int max_splits = (max_ctx + SPLIT_KEYS - 1) / SPLIT_KEYS;
+  const int G = n_heads / pv.n_kv_heads, hgroups = (G + 15) / 16;
+  const long long n_items = (long long)n_tokens * pv.n_kv_heads * hgroups * max_splits;
+  if (n_items > 0x7fffffff) return MF_ERR_BAD_ARG;
+  const int grid = n_items < n_sms ? (int)n_items : n_sms;
+  return (int)launch_dep(attn_decode_tma_kernel, dim3(grid), dim3((CW + 1) * 32), smem, stream, mk, mv, q, part_o,
+                         part_ml, positions, seq_of_token, pv, n_heads, n_tokens, scale * LOG2E, window, max_splits,
+                         status);
+}

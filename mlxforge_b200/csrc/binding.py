@@ -28,6 +28,7 @@ _SIGNATURES = {
                              c_float, c_int, _P],
     "mf_sample": [_P, c_int, c_int, c_longlong, _P, _P, _P, _P],
     "mf_set_pdl": [c_int],
+    "mf_set_decode_tma": [c_int, _P],
     "mf_gemm_bf16": [_P, _P, _P, c_int, c_int, c_int, c_int, _P, _P],
     "mf_stream_max_rows": [],
     "mf_stream_linear": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P],

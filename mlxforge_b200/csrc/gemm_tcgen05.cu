@@ -18,12 +18,8 @@
 //
 // The reference runs these products through its tensor library (`mx::matmul`,
 // src/model/decoder_model.cpp:191).
-#include <cuda.h>
-
-#include <mutex>
-#include <unordered_map>
-
 #include "common.cuh"
+#include "tma_host.cuh"
 
 namespace {
 
@@ -261,68 +257,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encoder() {
-  static EncodeTiled fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiled>(p);
-  });
-  return fn;
-}
-
-struct MapKey {
-  const void* ptr;
-  long long rows, k;
-  int box_rows;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows; }
-};
-struct MapHash {
-  size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.rows) * 31) ^ (std::hash<long long>()(k.k) * 131) ^
-           (size_t)k.box_rows;
-  }
-};
-
-// A [rows, k] row-major bfloat16 matrix as a tiled map with boxes of box_rows x 64 and 128-byte swizzle.
-int tensor_map(const void* ptr, long long rows, long long k, int box_rows, CUtensorMap* out) {
-  static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
-  static std::mutex mu;
-  std::lock_guard<std::mutex> lock(mu);
-  const MapKey key{ptr, rows, k, box_rows};
-  auto it = cache.find(key);
-  if (it != cache.end()) {
-    *out = it->second;
-    return 0;
-  }
-  EncodeTiled enc = encoder();
-  if (!enc) return MF_ERR_BAD_ARG;
-  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return 20000 + (int)r;
-  if (cache.size() > 4096) cache.clear();
-  cache.emplace(key, *out);
-  return 0;
-}
-
 template <int BN, int EPI>
 int launch(const void* A, const void* W, void* C, int M, int N, int K, int* status, cudaStream_t stream) {
   CUtensorMap ma, mw;
-  int rc = tensor_map(A, M, K, BM, &ma);
+  int rc = tma_host::bf16_map(A, M, K, BM, BK, &ma);
   if (rc) return rc;
-  rc = tensor_map(W, N, K, BN, &mw);
+  rc = tma_host::bf16_map(W, N, K, BN, BK, &mw);
   if (rc) return rc;
   const size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;

@@ -143,6 +143,7 @@ def skinny_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: b
 
 
 _STATUS = {}
+_TMA_STATUS_SET = False
 
 
 def kernel_status(device=None) -> torch.Tensor:
@@ -206,6 +207,12 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool 
                                  kernel_status(x.device).data_ptr(), _stream()), "gemm_bf16")
 
 
+def set_decode_tma(on: bool) -> bool:
+    """Switch the TMA decode-attention kernel (head size 64) on or off; returns the previous
+    setting.  Both kernels write the same partial results."""
+    return bool(library().mf_set_decode_tma(1 if on else 0, kernel_status().data_ptr()))
+
+
 def attention_decode_split(head_dim: int) -> int:
     """Keys per split of the decode kernel for a head size."""
     return int(library().mf_attention_decode_split(head_dim))
@@ -228,6 +235,10 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
         raise KernelError("attention_decode: bfloat16 only")
     n = q.shape[0]
+    global _TMA_STATUS_SET
+    if not _TMA_STATUS_SET:
+        library().mf_set_decode_tma(1, kernel_status(q.device).data_ptr())
+        _TMA_STATUS_SET = True
     need_o, need_ml = attention_decode_scratch(n, n_heads, head_dim, max_ctx)
     if part_o.numel() < need_o or part_ml.numel() < need_ml or part_o.dtype != torch.float32:
         raise KernelError("attention_decode: scratch too small")

@@ -197,8 +197,23 @@ def test_attention_generic(case, dtype):
         assert np.max(np.abs(got[i] - want)) < tol, (i, s, p)
 
 
-@pytest.mark.parametrize("case", ATTN_CASES)
-def test_attention_decode(case):
+@pytest.mark.parametrize("tma", [True, False])
+@pytest.mark.parametrize("case", ATTN_CASES + [(32, 8, 64, [2100, 700, 1, 513, 512], 0), (4, 1, 64, [900, 40], 300)])
+def test_attention_decode(case, tma):
+    import torch
+    from mlxforge_b200.csrc import ops
+    nh, nkv, hd, lengths, window = case
+    if not tma and hd != 64:
+        pytest.skip("only head size 64 has two kernels")
+    old = ops.set_decode_tma(tma)
+    try:
+        _attention_decode_case(case)
+        ops.check_kernel_status()
+    finally:
+        ops.set_decode_tma(old)
+
+
+def _attention_decode_case(case):
     import torch
     from mlxforge_b200.csrc import ops
     nh, nkv, hd, lengths, window = case
