@@ -3,13 +3,13 @@
 // It computes exactly what attn_decode_kernel (attention_decode.cu) computes and writes the
 // same per-split partial results (same split size, same merge kernel after it), but is built
 // around the memory system instead of around the warps:
-//   * one persistent block per SM walks work items (token, KV head x head group, split of 512
+//   * two persistent blocks per SM walk work items (token, KV head x head group, split of 512
 //     keys), item = block, block + grid, ...;
 //   * a producer warp issues one 2-D tensor copy per granule of 16 keys (a page holds whole
 //     granules, so a granule is 16 contiguous rows of the pool): 8 key boxes and 8 value boxes
 //     per stage of 128 keys, 128-byte swizzled, into a ring of STAGES stages, each signalled by
-//     an mbarrier; it runs ahead across item boundaries, so about 130 KB per SM are always on
-//     their way, and no thread computes an address per 16 bytes;
+//     an mbarrier; it runs ahead across item boundaries, so the two rings of an SM keep about
+//     130-190 KB on their way, and no thread computes an address per 16 bytes;
 //   * eight consumer warps take 16 keys of a stage each (scores and the second product on
 //     mma.sync as in the other kernel, softmax statistics in fp32, running over the item's
 //     stages), hand the stage back, and at the end of an item combine into one partial result.
@@ -26,7 +26,7 @@ constexpr int HD = 64;
 constexpr int TILE = 128;               // keys per stage: 8 granules of 16
 constexpr int GRAN_BYTES = 16 * HD * 2; // 2 KB: 16 rows of 128 bytes
 constexpr int STAGE_BYTES = 2 * 8 * GRAN_BYTES;   // keys then values: 32 KB
-constexpr int STAGES = 5;
+constexpr int STAGES = 3;                // per block; two blocks share an SM
 constexpr int SPLIT_KEYS = 512;
 constexpr int Q_BYTES = 16 * HD * 2;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -112,14 +112,15 @@ __global__ void __launch_bounds__((CW + 1) * 32)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __nv_bfloat16* __restrict__ q, float* __restrict__ part_o, float* __restrict__ part_ml,
                        const int* __restrict__ positions, const int* __restrict__ seq_of_token, PagedView pv,
-                       int n_heads, int n_tokens, float scale_log2, int window, int max_splits,
+                       int n_heads, int n_tokens, float scale_log2, int window, int max_splits, int comb_rows,
                        int* __restrict__ status) {
   extern __shared__ unsigned char raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
   unsigned char* ring = smem;                                             // [STAGES][K 8 x 2 KB | V 8 x 2 KB]
   unsigned char* q_s = smem + STAGES * STAGE_BYTES;                       // [2][16][64] bf16
-  float* comb = reinterpret_cast<float*>(q_s + 2 * Q_BYTES);              // [CW][16][HD + 2]: m, l, o[HD]
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(comb + CW * 16 * (HD + 2));
+  float* comb = reinterpret_cast<float*>(q_s + 2 * Q_BYTES);              // [CW][comb_rows][HD + 2]: m, l, o[HD]
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(comb + CW * comb_rows * (HD + 2));
+  const int CR = comb_rows;              // rows of the combine buffer per warp: the heads of a group
   const unsigned ring_u = smem_u32(ring), q_u = smem_u32(q_s), bars_u = smem_u32(bars);
   const unsigned full0 = bars_u, empty0 = bars_u + 8 * STAGES;
   const unsigned qfull0 = bars_u + 16 * STAGES, qempty0 = qfull0 + 16;
@@ -328,28 +329,28 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     // ---- combine the 8 warps into the item's partial result (rows of the group only)
     constexpr int CS = HD + 2;
     if (tq == 0) {
-      if (g < w.n_rows) { comb[(warp * 16 + g) * CS] = m_row[0]; comb[(warp * 16 + g) * CS + 1] = l_row[0]; }
-      if (g + 8 < w.n_rows) { comb[(warp * 16 + g + 8) * CS] = m_row[1]; comb[(warp * 16 + g + 8) * CS + 1] = l_row[1]; }
+      if (g < w.n_rows) { comb[(warp * CR + g) * CS] = m_row[0]; comb[(warp * CR + g) * CS + 1] = l_row[0]; }
+      if (g + 8 < w.n_rows) { comb[(warp * CR + g + 8) * CS] = m_row[1]; comb[(warp * CR + g + 8) * CS + 1] = l_row[1]; }
     }
 #pragma unroll
     for (int d = 0; d < HD / 8; d++) {
-      if (g < w.n_rows) *reinterpret_cast<float2*>(comb + (warp * 16 + g) * CS + 2 + d * 8 + tq * 2) = make_float2(o[d][0], o[d][1]);
+      if (g < w.n_rows) *reinterpret_cast<float2*>(comb + (warp * CR + g) * CS + 2 + d * 8 + tq * 2) = make_float2(o[d][0], o[d][1]);
       if (g + 8 < w.n_rows)
-        *reinterpret_cast<float2*>(comb + (warp * 16 + g + 8) * CS + 2 + d * 8 + tq * 2) = make_float2(o[d][2], o[d][3]);
+        *reinterpret_cast<float2*>(comb + (warp * CR + g + 8) * CS + 2 + d * 8 + tq * 2) = make_float2(o[d][2], o[d][3]);
     }
     consumer_sync();
     for (int i = threadIdx.x; i < w.n_rows * HD; i += CW * 32) {
       const int r = i / HD, d = i - r * HD;
       float M = -INFINITY;
 #pragma unroll
-      for (int cw = 0; cw < CW; cw++) M = fmaxf(M, comb[(cw * 16 + r) * CS]);
+      for (int cw = 0; cw < CW; cw++) M = fmaxf(M, comb[(cw * CR + r) * CS]);
       float L = 0.f, acc = 0.f;
 #pragma unroll
       for (int cw = 0; cw < CW; cw++) {
-        const float mw = comb[(cw * 16 + r) * CS];
+        const float mw = comb[(cw * CR + r) * CS];
         const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-        L += comb[(cw * 16 + r) * CS + 1] * f;
-        acc += comb[(cw * 16 + r) * CS + 2 + d] * f;
+        L += comb[(cw * CR + r) * CS + 1] * f;
+        acc += comb[(cw * CR + r) * CS + 2 + d] * f;
       }
       const long long row = ((long long)w.t * n_heads + w.head0 + r) * max_splits + w.split;
       part_o[row * HD + d] = acc;
@@ -376,11 +377,13 @@ int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
   if (rc) return rc;
   rc = tma_host::bf16_map(v_pool, pool_rows, HD, 16, HD, &mv);
   if (rc) return rc;
-  const size_t smem = (size_t)STAGES * STAGE_BYTES + 2 * Q_BYTES + (size_t)CW * 16 * (HD + 2) * 4 + (2 * STAGES + 4) * 8 + 1024;
+  const int G0 = n_heads / pv.n_kv_heads;
+  const int comb_rows = G0 < 16 ? G0 : 16;
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 2 * Q_BYTES + (size_t)CW * comb_rows * (HD + 2) * 4 + (2 * STAGES + 4) * 8 + 1024;
   static bool configured = false;
   static int n_sms = 0;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
     int dev = 0;
     e = cudaGetDevice(&dev);
@@ -392,8 +395,8 @@ int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
   const int G = n_heads / pv.n_kv_heads, hgroups = (G + 15) / 16;
   const long long n_items = (long long)n_tokens * pv.n_kv_heads * hgroups * max_splits;
   if (n_items > 0x7fffffff) return MF_ERR_BAD_ARG;
-  const int grid = n_items < n_sms ? (int)n_items : n_sms;
+  const int grid = n_items < 2 * n_sms ? (int)n_items : 2 * n_sms;
   return (int)launch_dep(attn_decode_tma_kernel, dim3(grid), dim3((CW + 1) * 32), smem, stream, mk, mv, q, part_o,
                          part_ml, positions, seq_of_token, pv, n_heads, n_tokens, scale * LOG2E, window, max_splits,
-                         status);
+                         comb_rows, status);
 }

@@ -98,5 +98,13 @@ def check(code: int, what: str, launches: int = 1) -> None:
         return
     if code in MF_ERRORS:
         raise KernelError(f"{what}: refused: {MF_ERRORS[code]}")
-    import torch
-    raise KernelError(f"{what}: CUDA error {code} ({torch.cuda.cudart().cudaGetErrorString(code) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else ''})")
+    raise KernelError(f"{what}: CUDA error {code} ({_cuda_error_name(code)})")
+
+
+def _cuda_error_name(code: int) -> str:
+    try:
+        import torch
+        rt = torch.cuda.cudart()
+        return str(rt.cudaGetErrorString(rt.cudaError(code)))
+    except Exception:
+        return "see cudaError_t"

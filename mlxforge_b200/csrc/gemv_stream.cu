@@ -216,7 +216,7 @@ int launch_one(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M,
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(stream_kernel<NB, ROWS, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+                                         (int)smem);   // smem depends on the template arguments only
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
