@@ -344,7 +344,7 @@ int launch_decode(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __n
 int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
                       float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv, long long pool_rows,
                       const int* positions, const int* seq_of_token, float scale, int window, int max_ctx,
-                      int* status, cudaStream_t stream);
+                      int* status, int* split_out, cudaStream_t stream);
 
 static int g_decode_tma = 1;
 static int* g_decode_status = nullptr;
@@ -358,7 +358,8 @@ MF_API int mf_set_decode_tma(int on, int* status) {
   return old;
 }
 
-// Keys per split for a head size (the caller sizes the scratch with it).
+// Fewest keys per split for a head size: the caller sizes the scratch with it (a launch may
+// choose longer splits and then uses less).
 MF_API int mf_attention_decode_split(int hd) {
   (void)hd;
   return SPLIT_KEYS;
@@ -380,13 +381,14 @@ MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_
   __nv_bfloat16* oo = (__nv_bfloat16*)out;
   if (hd == 64 && g_decode_tma) {
     // the map's row count only bounds the unit's own range check; rows beyond the pool are never asked for
+    int split = SPLIT_KEYS;
     const int rc = launch_decode_tma(qq, kk, vv, part_o, part_ml, n_tokens, n_heads, pv, 1ll << 28, positions,
-                                     seq_of_token, scale, window, max_ctx, g_decode_status, stream);
+                                     seq_of_token, scale, window, max_ctx, g_decode_status, &split, stream);
     if (rc == 0) {
-      const int max_splits = (max_ctx + SPLIT_KEYS - 1) / SPLIT_KEYS;
+      const int max_splits = (max_ctx + split - 1) / split;
       dim3 mgrid(n_tokens, n_heads);
       return (int)launch_dep(attn_decode_merge_kernel, mgrid, dim3(64), 0, stream, (const float*)part_o,
-                             (const float*)part_ml, oo, positions, n_heads, hd, window, max_splits, SPLIT_KEYS);
+                             (const float*)part_ml, oo, positions, n_heads, hd, window, max_splits, split);
     }
     if (rc != MF_ERR_BAD_ARG) return rc;
   }

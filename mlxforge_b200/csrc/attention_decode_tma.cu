@@ -27,8 +27,8 @@ constexpr int TILE = 128;               // keys per stage: 8 granules of 16
 constexpr int GRAN_BYTES = 16 * HD * 2; // 2 KB: 16 rows of 128 bytes
 constexpr int STAGE_BYTES = 2 * 8 * GRAN_BYTES;   // keys then values: 32 KB
 constexpr int STAGES = 3;                // per block; two blocks share an SM
-constexpr int SPLIT_KEYS = 512;
 constexpr int Q_BYTES = 16 * HD * 2;
+constexpr int MIN_SPLIT_KEYS = 512, MAX_SPLIT_KEYS = 2048;   // keys per work item: chosen per launch
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 
@@ -88,7 +88,8 @@ struct Item {
   bool live;
 };
 __device__ __forceinline__ Item make_item(int item, int max_splits, int groups, int hgroups, int G,
-                                          const int* positions, const int* seq_of_token, int window) {
+                                          const int* positions, const int* seq_of_token, int window,
+                                          int SPLIT_KEYS) {
   Item it;
   it.split = item % max_splits;
   const int rest = item / max_splits;
@@ -113,7 +114,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const __nv_bfloat16* __restrict__ q, float* __restrict__ part_o, float* __restrict__ part_ml,
                        const int* __restrict__ positions, const int* __restrict__ seq_of_token, PagedView pv,
                        int n_heads, int n_tokens, float scale_log2, int window, int max_splits, int comb_rows,
-                       int* __restrict__ status) {
+                       int split_keys, int* __restrict__ status) {
   extern __shared__ unsigned char raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
   unsigned char* ring = smem;                                             // [STAGES][K 8 x 2 KB | V 8 x 2 KB]
@@ -152,20 +153,24 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     // What the copies of an item need from memory (the token's position and sequence, and the
     // page of each of the split's 32 granules: lane l looks up granule l) is fetched one item
     // ahead, so that the ring never waits for a table lookup.
-    auto fetch = [&](int item, Item& w, int& row) {
-      w = make_item(item, max_splits, groups, hgroups, G, positions, seq_of_token, window);
-      const int key16 = w.split * SPLIT_KEYS + lane * 16;
-      row = -1;
-      if (w.live && key16 <= w.pos && key16 + 16 > w.lo) {
-        const int blk = key16 / pv.page_size;
-        const int page = pv.block_table[(long long)w.seq * pv.bt_stride + blk];
-        row = (page * pv.n_kv_heads + w.kvh) * pv.page_size + (key16 - blk * pv.page_size);
+    // a split has up to MAX_SPLIT_KEYS / 16 = 128 granules: four per lane
+    auto fetch = [&](int item, Item& w, int (&row)[4]) {
+      w = make_item(item, max_splits, groups, hgroups, G, positions, seq_of_token, window, split_keys);
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int key16 = w.split * split_keys + (j * 32 + lane) * 16;
+        row[j] = -1;
+        if (w.live && (j * 32 + lane) * 16 < split_keys && key16 <= w.pos && key16 + 16 > w.lo) {
+          const int blk = key16 / pv.page_size;
+          const int page = pv.block_table[(long long)w.seq * pv.bt_stride + blk];
+          row[j] = (page * pv.n_kv_heads + w.kvh) * pv.page_size + (key16 - blk * pv.page_size);
+        }
       }
     };
     unsigned it = 0, live_items = 0;
     int item = blockIdx.x;
     Item w, w_next;
-    int row = -1, row_next = -1;
+    int row[4] = {-1, -1, -1, -1}, row_next[4] = {-1, -1, -1, -1};
     w_next.live = false;
     if (item < n_items) fetch(item, w, row);
     while (item < n_items) {
@@ -185,8 +190,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           const unsigned s = it % STAGES, round = it / STAGES;
           // lanes 0..7: the key box of granule `lane`; lanes 8..15: its value box
           const int gran = lane & 7;
-          const int src_lane = (tile * TILE - w.split * SPLIT_KEYS) / 16 + gran;     // who looked this granule up
-          const int box_row = __shfl_sync(0xffffffffu, row, src_lane);
+          const int gi = (tile * TILE - w.split * split_keys) / 16 + gran;           // granule of the split
+          const int j = gi >> 5;                                                       // the same for the tile's 8
+          const int mine = j == 0 ? row[0] : (j == 1 ? row[1] : (j == 2 ? row[2] : row[3]));
+          const int box_row = __shfl_sync(0xffffffffu, mine, gi & 31);                 // from who looked it up
           const bool valid = lane < 16 && box_row >= 0;
           const unsigned n_valid = __popc(__ballot_sync(0xffffffffu, valid));
           if (lane == 0) {
@@ -201,7 +208,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
       }
       w = w_next;
-      row = row_next;
+#pragma unroll
+      for (int j = 0; j < 4; j++) row[j] = row_next[j];
       item = next;
     }
     return;
@@ -211,7 +219,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int g = lane >> 2, tq = lane & 3;
   unsigned it = 0, live_items = 0;
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-    const Item w = make_item(item, max_splits, groups, hgroups, G, positions, seq_of_token, window);
+    const Item w = make_item(item, max_splits, groups, hgroups, G, positions, seq_of_token, window, split_keys);
     if (!w.live) continue;
     // ---- the query tile as A fragments (read once per item)
     unsigned qa[HD / 16][4];
@@ -370,7 +378,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
                       float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv, long long pool_rows,
                       const int* positions, const int* seq_of_token, float scale, int window, int max_ctx,
-                      int* status, cudaStream_t stream) {
+                      int* status, int* split_out, cudaStream_t stream) {
   if (pv.head_dim != HD || pv.page_size % 16) return MF_ERR_BAD_ARG;
   CUtensorMap mk, mv;
   int rc = tma_host::bf16_map(k_pool, pool_rows, HD, 16, HD, &mk);
@@ -391,12 +399,20 @@ int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int max_splits = (max_ctx + SPLIT_KEYS - 1) / SPLIT_KEYS;
+  // Longer splits cost less per key (an item ends with a combine of the eight warps), shorter
+  // ones give more items: take the longest split that still gives most blocks an item.
   const int G = n_heads / pv.n_kv_heads, hgroups = (G + 15) / 16;
-  const long long n_items = (long long)n_tokens * pv.n_kv_heads * hgroups * max_splits;
+  int split_keys = MAX_SPLIT_KEYS;
+  long long n_items = 0;
+  for (;; split_keys /= 2) {
+    n_items = (long long)n_tokens * pv.n_kv_heads * hgroups * ((max_ctx + split_keys - 1) / split_keys);
+    if (split_keys == MIN_SPLIT_KEYS || n_items * 20 >= (long long)2 * n_sms * 17) break;
+  }
+  *split_out = split_keys;
+  const int max_splits = (max_ctx + split_keys - 1) / split_keys;
   if (n_items > 0x7fffffff) return MF_ERR_BAD_ARG;
   const int grid = n_items < 2 * n_sms ? (int)n_items : 2 * n_sms;
   return (int)launch_dep(attn_decode_tma_kernel, dim3(grid), dim3((CW + 1) * 32), smem, stream, mk, mv, q, part_o,
                          part_ml, positions, seq_of_token, pv, n_heads, n_tokens, scale * LOG2E, window, max_splits,
-                         comb_rows, status);
+                         comb_rows, split_keys, status);
 }

@@ -116,7 +116,8 @@ class ModelRunner:
                 raise IndexError(f"token id {lo if lo < 0 else hi} is outside the vocabulary [0, {self.vocab})")
         self.cache.reserve([(e.seq, len(e.tokens)) for e in entries])
         graphed = self.cuda_graphs and all(len(e.tokens) == 1 for e in entries)
-        batch = self._build(entries, pad_tables=graphed)
+        decode_only = all(len(e.tokens) == 1 for e in entries)
+        batch = self._build(entries, pad_tables=decode_only)
         logits = self._forward_graphed(batch) if graphed else self.model.forward(batch, self.cache)
         for e in entries:
             self.cache.commit(e.seq, len(e.tokens))
@@ -190,7 +191,9 @@ class ModelRunner:
         for g in range(len(self.cache.pools)):
             width = max(1, max(len(entries[i].seq.blocks[g]) for i in order))
             if pad_tables:
-                # a graph serves every step whose tables fit its width: powers of two from 16 up
+                # decode-only steps: widths in powers of two from 16 up, so that one CUDA graph serves
+                # every step whose tables fit, and so that an eager step and a replayed one size
+                # (and split) their attention alike
                 width = max(16, 1 << (width - 1).bit_length())
                 b.max_ctx = max(b.max_ctx, width * self.cache.page_size)
             tab = np.full((R, width), -1, dtype=np.int32)
