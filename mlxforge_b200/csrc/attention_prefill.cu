@@ -1,5 +1,5 @@
 // Causal GQA attention of prompt portions (two or more new tokens per sequence)
-// over the paged bfloat16 cache: one block per (64 queries, query head, sequence),
+// over the paged bfloat16 cache: one block per (128 or 64 queries, query head, sequence),
 // key tiles of 64 double-buffered through shared memory with cp.async, both
 // products on the tensor cores (mma.sync m16n8k16, bf16 in, fp32 out), online
 // softmax in fp32.  The new tokens' own keys are already in the cache (the rotary
@@ -17,7 +17,6 @@
 
 namespace {
 
-constexpr int BM = 64;      // queries per block (16 per warp)
 constexpr int BN = 64;      // keys per tile
 constexpr int WARPS = 4;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -51,6 +50,16 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// MT: 16-row query tiles per warp (2 for head sizes up to 128: the fragments of a key tile are
+// then read from shared memory once for 32 queries; 1 above, where registers run out).
+template <int HD_MAX> struct Shape { static constexpr int MT = 1; };
+
 template <int HD_MAX>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
@@ -59,12 +68,15 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const int* __restrict__ seq_ctx_len, int table_row0, PagedView pv, int n_heads,
                     float scale_log2, int window) {
   constexpr int DT = HD_MAX / 8;
+  constexpr int MT = Shape<HD_MAX>::MT;
+  constexpr int BM = WARPS * 16 * MT;                          // queries per block
   const int hd = pv.head_dim, ld = hd + 8, chunks = hd >> 3;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [BM][ld]
   __nv_bfloat16* kv_s = q_s + BM * ld;                                    // [2 stages][K, V][BN][ld]
 
-  const int tile = blockIdx.x, head = blockIdx.y, s = blockIdx.z;
+  // the heaviest tiles (the last queries of a portion see the most keys) are launched first
+  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, head = blockIdx.y, s = blockIdx.z;
   const int q_len = seq_q_len[s];
   if (tile * BM >= q_len) return;
   const int q_start = seq_q_start[s], ctx = seq_ctx_len[s];
@@ -107,14 +119,25 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   load_kv(kt0, 0);
   cp_async_commit();
 
-  float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
-  float o[DT][4];
+  // this warp's queries: MT tiles of 16 rows; thread rows g and g + 8 of each
+  const int wrow0 = warp * 16 * MT;
+  float m_row[MT][2], l_row[MT][2];
+  float o[MT][DT][4];
+  int my_pos[MT][2], my_lo[MT][2];
 #pragma unroll
-  for (int d = 0; d < DT; d++) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
-  const int my_pos[2] = {pos_first + warp * 16 + g, pos_first + warp * 16 + g + 8};
-  int my_lo[2];
+  for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
-  for (int h = 0; h < 2; h++) my_lo[h] = (window > 0 && my_pos[h] - window + 1 > 0) ? my_pos[h] - window + 1 : 0;
+    for (int h = 0; h < 2; h++) {
+      m_row[mt][h] = -INFINITY;
+      l_row[mt][h] = 0.f;
+      my_pos[mt][h] = pos_first + wrow0 + mt * 16 + g + h * 8;
+      my_lo[mt][h] = (window > 0 && my_pos[mt][h] - window + 1 > 0) ? my_pos[mt][h] - window + 1 : 0;
+    }
+#pragma unroll
+    for (int d = 0; d < DT; d++) o[mt][d][0] = o[mt][d][1] = o[mt][d][2] = o[mt][d][3] = 0.f;
+  }
+  const int w_pos_first = pos_first + wrow0, w_pos_last = w_pos_first + 16 * MT - 1;
+  const int w_lo_last = (window > 0 && w_pos_last - window + 1 > 0) ? w_pos_last - window + 1 : 0;
 
   for (int kt = kt0; kt <= kt1; kt++) {
     const int stage = (kt - kt0) & 1;
@@ -125,87 +148,107 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     const __nv_bfloat16* k_s = kv_s + (stage * 2 + 0) * BN * ld;
     const __nv_bfloat16* v_s = kv_s + (stage * 2 + 1) * BN * ld;
 
-    // a warp whose 16 queries all lie before this key tile has nothing to do in it
-    const bool active = kt * BN <= pos_first + warp * 16 + 15;
+    // a warp whose queries all lie before this key tile has nothing to do in it
+    const bool active = kt * BN <= w_pos_last;
     if (active) {
-      float sc[BN / 8][4];
+      float sc[MT][BN / 8][4];
 #pragma unroll
-      for (int j = 0; j < BN / 8; j++) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+      for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int j = 0; j < BN / 8; j++) sc[mt][j][0] = sc[mt][j][1] = sc[mt][j][2] = sc[mt][j][3] = 0.f;
 #pragma unroll
       for (int kk = 0; kk < HD_MAX / 16; kk++) {
         if (kk * 16 < hd) {
-          unsigned a[4];
-          ldmatrix_x4(a, q_s + (warp * 16 + (lane & 15)) * ld + kk * 16 + (lane >> 4) * 8);
+          unsigned a[MT][4];
+#pragma unroll
+          for (int mt = 0; mt < MT; mt++)
+            ldmatrix_x4(a[mt], q_s + (wrow0 + mt * 16 + (lane & 15)) * ld + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
           for (int j = 0; j < BN / 8; j += 2) {
             unsigned b[4];
             const int mi = lane >> 3, r = lane & 7;
             ldmatrix_x4(b, k_s + (j * 8 + (mi >> 1) * 8 + r) * ld + kk * 16 + (mi & 1) * 8);
-            mma_bf16(sc[j], a, b[0], b[1]);
-            mma_bf16(sc[j + 1], a, b[2], b[3]);
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+              mma_bf16(sc[mt][j], a[mt], b[0], b[1]);
+              mma_bf16(sc[mt][j + 1], a[mt], b[2], b[3]);
+            }
           }
         }
       }
-      // ---- scale, mask (causal, window), online softmax
-      float mx[2] = {-INFINITY, -INFINITY};
+      // ---- mask only where the tile touches the diagonal or an end of a window; online softmax
+      const bool edge = kt * BN + BN - 1 > w_pos_first || kt * BN < w_lo_last;
 #pragma unroll
-      for (int j = 0; j < BN / 8; j++) {
+      for (int mt = 0; mt < MT; mt++) {
+        float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const int key = kt * BN + j * 8 + tq * 2 + (e & 1);
-          const int h = e >> 1;
-          const float v = (key <= my_pos[h] && key >= my_lo[h]) ? sc[j][e] * scale_log2 : -INFINITY;
-          sc[j][e] = v;
-          mx[h] = fmaxf(mx[h], v);
+        for (int j = 0; j < BN / 8; j++) {
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            float v = sc[mt][j][e];
+            if (edge) {
+              const int key = kt * BN + j * 8 + tq * 2 + (e & 1);
+              if (key > my_pos[mt][e >> 1] || key < my_lo[mt][e >> 1]) v = -INFINITY;
+              sc[mt][j][e] = v;
+            }
+            mx[e >> 1] = fmaxf(mx[e >> 1], v);
+          }
         }
-      }
-      float alpha[2], m_use[2];
+        float alpha[2], m_off[2];
 #pragma unroll
-      for (int h = 0; h < 2; h++) {
-        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-        const float m_new = fmaxf(m_row[h], mx[h]);
-        m_use[h] = (m_new == -INFINITY) ? 0.f : m_new;
-        alpha[h] = (m_row[h] == -INFINITY) ? 0.f : exp2f(m_row[h] - m_use[h]);
-        m_row[h] = m_new;
-      }
-      float sum[2] = {0.f, 0.f};
-#pragma unroll
-      for (int j = 0; j < BN / 8; j++) {
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const float p = exp2f(sc[j][e] - m_use[e >> 1]);
-          sc[j][e] = p;
-          sum[e >> 1] += p;
+        for (int h = 0; h < 2; h++) {
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+          mx[h] *= scale_log2;                                        // scale > 0: the max commutes with it
+          const float m_new = fmaxf(m_row[mt][h], mx[h]);
+          m_off[h] = (m_new == -INFINITY) ? 0.f : m_new;
+          alpha[h] = (m_row[mt][h] == -INFINITY) ? 0.f : ex2(m_row[mt][h] - m_off[h]);
+          m_row[mt][h] = m_new;
         }
-      }
+        float sum[2] = {0.f, 0.f};
 #pragma unroll
-      for (int h = 0; h < 2; h++) {
-        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
-        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
-        l_row[h] = l_row[h] * alpha[h] + sum[h];
-      }
+        for (int j = 0; j < BN / 8; j++) {
 #pragma unroll
-      for (int d = 0; d < DT; d++) {
-        o[d][0] *= alpha[0]; o[d][1] *= alpha[0];
-        o[d][2] *= alpha[1]; o[d][3] *= alpha[1];
+          for (int e = 0; e < 4; e++) {
+            const float p = ex2(fmaf(sc[mt][j][e], scale_log2, -m_off[e >> 1]));   // one multiply-add, one ex2
+            sc[mt][j][e] = p;
+            sum[e >> 1] += p;
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
+          sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
+          l_row[mt][h] = l_row[mt][h] * alpha[h] + sum[h];
+        }
+#pragma unroll
+        for (int d = 0; d < DT; d++) {
+          o[mt][d][0] *= alpha[0]; o[mt][d][1] *= alpha[0];
+          o[mt][d][2] *= alpha[1]; o[mt][d][3] *= alpha[1];
+        }
       }
       // ---- O += P V
 #pragma unroll
       for (int kk = 0; kk < BN / 16; kk++) {
-        unsigned a[4];
-        a[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
-        a[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
-        a[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
-        a[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+        unsigned a[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+          a[mt][0] = pack_bf16(sc[mt][2 * kk][0], sc[mt][2 * kk][1]);
+          a[mt][1] = pack_bf16(sc[mt][2 * kk][2], sc[mt][2 * kk][3]);
+          a[mt][2] = pack_bf16(sc[mt][2 * kk + 1][0], sc[mt][2 * kk + 1][1]);
+          a[mt][3] = pack_bf16(sc[mt][2 * kk + 1][2], sc[mt][2 * kk + 1][3]);
+        }
 #pragma unroll
         for (int d = 0; d < DT; d += 2) {
           if (d * 8 < hd) {
             unsigned b[4];
             const int mi = lane >> 3, r = lane & 7;
             ldmatrix_x4_trans(b, v_s + (kk * 16 + (mi & 1) * 8 + r) * ld + d * 8 + (mi >> 1) * 8);
-            mma_bf16(o[d], a, b[0], b[1]);
-            mma_bf16(o[d + 1], a, b[2], b[3]);
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+              mma_bf16(o[mt][d], a[mt], b[0], b[1]);
+              mma_bf16(o[mt][d + 1], a[mt], b[2], b[3]);
+            }
           }
         }
       }
@@ -216,15 +259,19 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 
   // ---- normalise and store (rows of the portion only)
 #pragma unroll
-  for (int h = 0; h < 2; h++) {
-    const int r = warp * 16 + g + h * 8;
-    if (r >= rows) continue;
-    const float inv = 1.0f / l_row[h];
-    __nv_bfloat16* orow = out + ((long long)(q_start + tile * BM + r) * n_heads + head) * hd;
+  for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
-    for (int d = 0; d < DT; d++) {
-      if (d * 8 < hd) {
-        *reinterpret_cast<unsigned*>(orow + d * 8 + tq * 2) = pack_bf16(o[d][h * 2] * inv, o[d][h * 2 + 1] * inv);
+    for (int h = 0; h < 2; h++) {
+      const int r = wrow0 + mt * 16 + g + h * 8;
+      if (r >= rows) continue;
+      const float inv = 1.0f / l_row[mt][h];
+      __nv_bfloat16* orow = out + ((long long)(q_start + tile * BM + r) * n_heads + head) * hd;
+#pragma unroll
+      for (int d = 0; d < DT; d++) {
+        if (d * 8 < hd) {
+          *reinterpret_cast<unsigned*>(orow + d * 8 + tq * 2) =
+              pack_bf16(o[mt][d][h * 2] * inv, o[mt][d][h * 2 + 1] * inv);
+        }
       }
     }
   }
@@ -235,6 +282,7 @@ int launch_prefill(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __
                    __nv_bfloat16* out, const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len,
                    int table_row0, int n_seqs, int max_q_len, int n_heads, PagedView pv, float scale, int window,
                    cudaStream_t stream) {
+  constexpr int BM = WARPS * 16 * Shape<HD_MAX>::MT;
   const int ld = pv.head_dim + 8;
   const size_t smem = (size_t)(BM * ld + 4 * BN * ld) * sizeof(__nv_bfloat16);
   static bool configured = false;
