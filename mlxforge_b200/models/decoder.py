@@ -68,7 +68,7 @@ class DecoderModel:
         return specs
 
     def load(self, model_dir: str) -> None:
-        tensors = load_tensors(model_dir, self.tensor_specs(), self.rt.device)
+        tensors = load_tensors(model_dir, self.tensor_specs(), self.rt.device, exact=self.rt.precise)
         self.bind(tensors)
 
     def bind(self, tensors) -> None:

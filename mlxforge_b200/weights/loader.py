@@ -61,11 +61,12 @@ def check_names(specs: Dict[str, TensorSpec], found: Dict[str, tuple], where: st
         raise WeightError(missing, unexpected, wrong, where)
 
 
-def _to_torch(a: np.ndarray, tag: str) -> torch.Tensor:
+def _to_torch(a: np.ndarray, tag: str, exact: bool = False) -> torch.Tensor:
     if tag == "BF16":
         return torch.from_numpy(a.copy()).view(torch.bfloat16)
     if tag == "F16":
-        return torch.from_numpy(a.copy()).to(torch.bfloat16)
+        # float16 is no subset of bfloat16: the 32-bit path upcasts it exactly instead
+        return torch.from_numpy(a.copy()).to(torch.float32 if exact else torch.bfloat16)
     if tag == "F32":
         return torch.from_numpy(a.copy())
     if tag == "F64":
@@ -75,8 +76,9 @@ def _to_torch(a: np.ndarray, tag: str) -> torch.Tensor:
     raise ValueError(tag)
 
 
-def load_tensors(model_dir: str, specs: Dict[str, TensorSpec], device) -> Dict[str, torch.Tensor]:
-    """Read every declared tensor of ``model_dir`` onto ``device``."""
+def load_tensors(model_dir: str, specs: Dict[str, TensorSpec], device, exact: bool = False) -> Dict[str, torch.Tensor]:
+    """Read every declared tensor of ``model_dir`` onto ``device``.  ``exact``: the
+    caller computes in 32-bit, so nothing may lose bits on the way in."""
     files = [SafetensorsFile(p) for p in model_files(model_dir)]
     try:
         entries = {}
@@ -91,7 +93,7 @@ def load_tensors(model_dir: str, specs: Dict[str, TensorSpec], device) -> Dict[s
             if name not in entries:
                 continue
             f, e = entries[name]
-            out[name] = _to_torch(f.array(e), e.dtype).to(device)
+            out[name] = _to_torch(f.array(e), e.dtype, exact).to(device)
         return out
     finally:
         for f in files:

@@ -34,9 +34,15 @@ TINY_C = {   # sizes that are no power of two anywhere: MHA 5:5, head_dim 48, od
     "rope_scaling": {"rope_type": "linear", "factor": 2.0},
     "max_position_embeddings": 512, "rms_norm_eps": 3e-5, "tie_word_embeddings": False,
 }
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-SEEDS = {"A": 0, "B": 1, "C": 2}
-NORM_STD = {"A": 0.0, "B": 0.1, "C": 0.2}
+TINY_D = {   # a width, an intermediate size and a vocabulary that are no multiple of 8: the scalar kernel paths
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 3, "num_key_value_heads": 3,
+    "head_dim": 16, "intermediate_size": 52, "vocab_size": 131, "rope_theta": 20000.0,
+    "max_position_embeddings": 256, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
+NORM_STD = {"A": 0.0, "B": 0.1, "C": 0.2, "D": 0.05}
 
 
 def tensor_shapes(cfg):

@@ -21,7 +21,7 @@ pytestmark = pytest.mark.gpu
 TOL_F32 = 1e-4
 BF16_NOISE_FACTOR = 3.0
 
-LENGTHS = {"A": [5, 17, 31, 70], "B": [1, 9, 40, 70, 131], "C": [3, 33, 64, 97]}
+LENGTHS = {"A": [5, 17, 31, 70], "B": [1, 9, 40, 70, 131], "C": [3, 33, 64, 97], "D": [2, 19, 66]}
 
 
 def _requests(cfg, which):
