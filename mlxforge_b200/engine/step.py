@@ -12,6 +12,8 @@ position and sequence index, and a block table per sequence and cache group.
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -86,6 +88,8 @@ class ModelRunner:
         self._copy_pending = False
         self.last_meta_bytes = 0
         self.steps = 0
+        self._last: Optional[dict] = None     # the last decode-only step's metadata, for _advance
+        self._plain_groups = all(g.need.window == 0 for g in cache.layout.paged)
         # CUDA graphs of decode-only steps, keyed by the shape of the step's metadata
         self._graphs: Dict[tuple, tuple] = {}
         self._warm: set = set()
@@ -145,8 +149,16 @@ class ModelRunner:
             self._graphs.clear()
         graph = torch.cuda.CUDAGraph()
         before = binding.launch_count()
-        with torch.cuda.graph(graph):
-            logits = self.model.forward(batch, self.cache)
+        # Nothing may free device or pinned memory while the stream is capturing (the allocators
+        # then touch events, which invalidates the capture): keep the collector out of it.
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(batch, self.cache)
+        finally:
+            if gc_was_on:
+                gc.enable()
         nodes = binding.launch_count() - before
         binding.count_launches(-nodes)          # capturing launched nothing
         self._graphs[key] = ((self.rt.generation, self._meta.data_ptr()), graph, logits, nodes)
@@ -155,12 +167,55 @@ class ModelRunner:
         self.graph_replays += 1
         return logits
 
+    def _advance(self, entries: Sequence[StepEntry]) -> Optional[StepBatch]:
+        """Steady decoding: the same sequences as in the last step, one token each, the same
+        wanted rows, no window anywhere, tables still within their width.  The metadata then
+        differs from the last step's only in the tokens, in positions and lengths (one more)
+        and in the block-table entries of sequences that got a new page; it is patched in
+        place in the pinned buffer instead of being built again.  None if this is not that case."""
+        last = self._last
+        if last is None or len(entries) != len(last["seq_ids"]):
+            return None
+        for e, sid, want in zip(entries, last["seq_ids"], last["wants"]):
+            if e.seq.seq_id != sid or len(e.tokens) != 1 or tuple(e.want) != want:
+                return None
+        b: StepBatch = last["batch"]
+        for g, width in enumerate(last["widths"]):
+            for e in entries:
+                if len(e.seq.blocks[g]) > width:
+                    return None
+        if self._copy_pending:
+            self._copied.synchronize()
+        v = last["host"]
+        v["tokens"][:] = [e.tokens[0] for e in entries]
+        v["positions"] += 1
+        v["ctx_len"] += 1
+        b.ctx_len = [c + 1 for c in b.ctx_len]
+        for g, tab in enumerate(v["tables"]):
+            counts = last["counts"][g]
+            for row, e in enumerate(entries):
+                n = len(e.seq.blocks[g])
+                if n != counts[row]:
+                    tab[row, counts[row]:n] = e.seq.row(g)[counts[row]:n]
+                    counts[row] = n
+        total = last["total"]
+        self.last_meta_bytes = total * 4
+        self._meta[:total].copy_(self._pinned[:total], non_blocking=True)
+        self._copied.record()
+        self._copy_pending = True
+        return b
+
     def _build(self, entries: Sequence[StepEntry], pad_tables: bool = False) -> StepBatch:
+        if pad_tables and self._plain_groups:
+            fast = self._advance(entries)
+            if fast is not None:
+                return fast
+        self._last = None
         order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
         b = StepBatch()
-        b.runner = self
+        b.runner = weakref.proxy(self)      # no cycle: the runner keeps the last batch (see _advance)
         b.n_seqs, b.n_tokens = R, T
         tokens = np.empty(T, dtype=np.int32)
         positions = np.empty(T, dtype=np.int32)
@@ -226,6 +281,16 @@ class ModelRunner:
          b.seq_ctx_len) = views[:8]
         for g, tab in enumerate(tables):
             b._block_tables[g] = views[8 + g].view(tab.shape)
+        if pad_tables and self._plain_groups:
+            def hv(i):
+                return host[offsets[i]:offsets[i] + parts[i].size]
+            self._last = {
+                "seq_ids": [e.seq.seq_id for e in entries], "wants": [tuple(e.want) for e in entries],
+                "batch": b, "total": total, "widths": [tab.shape[1] for tab in tables],
+                "counts": [[len(e.seq.blocks[g]) for e in entries] for g in range(len(tables))],
+                "host": {"tokens": hv(0), "positions": hv(1), "ctx_len": hv(7),
+                         "tables": [hv(8 + g).reshape(tab.shape) for g, tab in enumerate(tables)]},
+            }
         return b
 
     def _ensure_meta(self, n: int) -> None:
@@ -234,6 +299,7 @@ class ModelRunner:
                 self._copied.synchronize()
                 self._copy_pending = False
             cap = max(4096, 2 * n)
+            self._last = None
             self._pinned = torch.empty(cap, dtype=torch.int32, pin_memory=True)
             self._meta = torch.empty(cap, dtype=torch.int32, device=self.rt.device)
 
