@@ -145,8 +145,12 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   for (int i = threadIdx.x; i < 2 * Q_BYTES / 16; i += blockDim.x) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");    // before the copy unit writes there
   __syncthreads();
-  pdl_wait();                       // q and the newest keys and values come from the kernel before
-  if (threadIdx.x == 0) pdl_launch();
+  // q and each token's newest key and value come from the kernel before this one; everything
+  // older in the cache does not, so the producer starts filling its ring before it waits
+  if (warp != CW) {
+    pdl_wait();
+    if (threadIdx.x == 0) pdl_launch();
+  }
 
   if (warp == CW) {
     // ------------------------------------------------------------ producer warp
@@ -168,6 +172,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       }
     };
     unsigned it = 0, live_items = 0;
+    bool waited = false;
     int item = blockIdx.x;
     Item w, w_next;
     int row[4] = {-1, -1, -1, -1}, row_next[4] = {-1, -1, -1, -1};
@@ -177,17 +182,30 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       const int next = item + gridDim.x;
       if (next < n_items) fetch(next, w_next, row_next);
       if (w.live) {
-        // the item's queries: G contiguous rows
-        if (lane == 0) {
-          const unsigned b = live_items & 1, use = live_items >> 1;
-          if (use > 0) mbar_wait(qempty0 + 8 * b, (use - 1) & 1, status, 21);
-          mbar_expect_tx(qfull0 + 8 * b, (unsigned)w.n_rows * HD * 2);
-          bulk_copy(q_u + b * Q_BYTES, q + ((long long)w.t * n_heads + w.head0) * HD, (unsigned)w.n_rows * HD * 2,
-                    qfull0 + 8 * b);
-        }
+        // the item's queries: G contiguous rows (only after the wait: the kernel before wrote them)
+        const unsigned qb = live_items & 1, quse = live_items >> 1;
+        auto issue_q = [&]() {
+          if (lane == 0) {
+            if (quse > 0) mbar_wait(qempty0 + 8 * qb, (quse - 1) & 1, status, 21);
+            mbar_expect_tx(qfull0 + 8 * qb, (unsigned)w.n_rows * HD * 2);
+            bulk_copy(q_u + qb * Q_BYTES, q + ((long long)w.t * n_heads + w.head0) * HD,
+                      (unsigned)w.n_rows * HD * 2, qfull0 + 8 * qb);
+          }
+        };
+        bool q_done = false;
         live_items++;
         for (int tile = w.tile0; tile <= w.tile1; tile++, it++) {
           const unsigned s = it % STAGES, round = it / STAGES;
+          // Before the wait only tiles of older keys may be fetched, and only while the ring has
+          // room (the consumers cannot free a stage before they have their queries).
+          if (!waited && ((tile + 1) * TILE > w.pos || round > 0)) {
+            pdl_wait();
+            waited = true;
+          }
+          if (waited && !q_done) {
+            issue_q();
+            q_done = true;
+          }
           // lanes 0..7: the key box of granule `lane`; lanes 8..15: its value box
           const int gran = lane & 7;
           const int gi = (tile * TILE - w.split * split_keys) / 16 + gran;           // granule of the split
@@ -206,12 +224,20 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             tma_load_2d(dst, lane < 8 ? &map_k : &map_v, 0, box_row, full0 + 8 * s);
           }
         }
+        if (!q_done) {
+          if (!waited) {
+            pdl_wait();
+            waited = true;
+          }
+          issue_q();
+        }
       }
       w = w_next;
 #pragma unroll
       for (int j = 0; j < 4; j++) row[j] = row_next[j];
       item = next;
     }
+    if (!waited) pdl_wait();
     return;
   }
 
