@@ -31,6 +31,7 @@ _SIGNATURES = {
     "mf_set_decode_tma": [c_int, _P],
     "mf_gemm_bf16": [_P, _P, _P, c_int, c_int, c_int, c_int, _P, _P],
     "mf_stream_max_rows": [],
+    "mf_set_stream_tensor_copies": [c_int],
     "mf_stream_linear": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "mf_skinny_max_rows": [],
     "mf_skinny_linear": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],

@@ -13,9 +13,8 @@
 //   * eight consumer warps wait for a buffer, read their 64-element slice of every row
 //     straight from it (rows are padded so that the 16-byte reads hit distinct banks),
 //     multiply, and hand the buffer back through a second mbarrier.
-// The bytes in flight per SM are set by the ring (about 87 KB per block), not by registers.
-// One block runs per SM; with ~104 KB of shared memory each, the block of the next product
-// of the step is resident beside it and has its ring full when this one ends.
+// Two blocks run per SM.  Widths that are a whole number of stages take the second kernel of
+// this file, which brings a stage with one tensor copy instead of sixteen row-segment copies.
 //
 // The producer starts before the kernel that makes x has finished (weights never change);
 // consumers wait for it before they read x.  Every mbarrier wait is bounded: after
@@ -25,8 +24,11 @@
 // Reference: the hand-written few-row products of hvasconcelos/mlxforge,
 // src/model/skinny_matmul.cpp:17-140 (weights streamed once, fp32 accumulation).
 #include "common.cuh"
+#include "tma_host.cuh"
 
 namespace {
+
+int g_stream_tensor_copies = 1;     // 0: row-segment copies for every width (mf_set_stream_tensor_copies)
 
 constexpr int CW = 8;                 // consumer warps
 constexpr int KT = 512;               // elements of K per stage
@@ -208,6 +210,171 @@ stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The same product with ONE tensor copy per stage.  Row segments of 1 KB cost the copy engine an
+// instruction each, and at sixteen per stage it is the rate of those, not HBM, that bounds the
+// stream (about 6.0 TB/s here against 7.0 with one 16 KB copy).  The matrix is described to the
+// engine as [K/64 chunks][N rows][64 elements]; a box of (8 chunks x 16 rows) or (16 chunks x 8
+// rows) is one stage, stored [chunk][row][128 bytes] with the 128-byte swizzle, which also keeps
+// the fragment reads off each other's banks: a thread takes the 16-byte pieces 2t and 2t+1 of
+// its warp's chunk, so the eight threads of a quarter-warp (rows g, g+1) touch eight different
+// pieces.  Needs K to be a whole number of stages; other widths take the kernel above.
+constexpr int T_STAGES = 3;
+constexpr int T_STAGE_BYTES = 16384;
+
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+template <int NB, int ROWS, typename OutT>
+__global__ void __launch_bounds__((CW + 1) * 32)
+stream_tmap_kernel(const __nv_bfloat16* __restrict__ x, const __grid_constant__ CUtensorMap map,
+                   OutT* __restrict__ out, int M, int N, int K, int mode, int* __restrict__ status) {
+  constexpr int SUB = 16 / ROWS;                 // chunks of 64 per warp and stage (1 or 2)
+  constexpr int KSTAGE = 512 * SUB;              // elements of K per stage
+  constexpr int CHUNK_BYTES = ROWS * 128;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + T_STAGES * T_STAGE_BYTES);
+  float* red = reinterpret_cast<float*>(bars + 2 * T_STAGES);                                      // [CW][ROWS][NB*8+1]
+  constexpr int RED_M = NB * 8 + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (N + ROWS - 1) / ROWS, n_ks = (K + KSTAGE - 1) / KSTAGE;
+  const unsigned ring_u = smem_u32(smem), bars_u = smem_u32(bars);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T_STAGES; s++) {
+      mbar_init(bars_u + 8 * s, 1);
+      mbar_init(bars_u + 8 * (T_STAGES + s), CW);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == CW) {
+    if (lane == 0) {
+      unsigned it = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        for (int ks = 0; ks < n_ks; ks++, it++) {
+          const unsigned s = it % T_STAGES, round = it / T_STAGES;
+          if (round > 0) mbar_wait(bars_u + 8 * (T_STAGES + s), (round - 1) & 1, status, 1);
+          mbar_expect_tx(bars_u + 8 * s, T_STAGE_BYTES);       // rows outside the matrix arrive as zeros
+          tma_load_3d(ring_u + s * T_STAGE_BYTES, &map, 0, tile * ROWS, ks * (KSTAGE / 64), bars_u + 8 * s);
+        }
+      }
+    }
+    return;
+  }
+
+  const int g = lane >> 2, t = lane & 3;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  pdl_wait();                // x comes from the kernel before this one
+  if (threadIdx.x == 0) pdl_launch();
+  unsigned it = 0;
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int n0 = tile * ROWS;
+    float acc[NB][4];
+#pragma unroll
+    for (int nb = 0; nb < NB; nb++) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f;
+
+    for (int ks = 0; ks < n_ks; ks++, it++) {
+      const unsigned s = it % T_STAGES, round = it / T_STAGES;
+      // x first (it does not wait for the weights): pieces 2t and 2t+1 of this warp's chunk(s)
+      uint4 xv[SUB][2][NB];
+#pragma unroll
+      for (int h = 0; h < SUB; h++)
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          const int k = ks * KSTAGE + (warp + CW * h) * 64 + (2 * t + c) * 8;
+#pragma unroll
+          for (int nb = 0; nb < NB; nb++) {
+            const int m = nb * 8 + g;
+            xv[h][c][nb] = (k < K && m < M) ? __ldg(reinterpret_cast<const uint4*>(x + (long long)m * K + k)) : zero;
+          }
+        }
+      mbar_wait(bars_u + 8 * s, round & 1, status, 2);
+#pragma unroll
+      for (int h = 0; h < SUB; h++) {
+        const unsigned base = ring_u + s * T_STAGE_BYTES + (warp + CW * h) * CHUNK_BYTES + g * 128;
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          const unsigned piece = (unsigned)((2 * t + c) ^ g) << 4;
+          const uint4 a = lds128(base + piece);
+          const uint4 b = ROWS == 16 ? lds128(base + 1024 + piece) : zero;
+#pragma unroll
+          for (int nb = 0; nb < NB; nb++) {
+            mma_bf16(acc[nb], a.x, b.x, a.y, b.y, xv[h][c][nb].x, xv[h][c][nb].y);
+            mma_bf16(acc[nb], a.z, b.z, a.w, b.w, xv[h][c][nb].z, xv[h][c][nb].w);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars_u + 8 * (T_STAGES + s));
+    }
+
+    // ---- sum the 8 warps' partial results in a fixed order
+#pragma unroll
+    for (int nb = 0; nb < NB; nb++) {
+      red[(warp * ROWS + g) * RED_M + nb * 8 + 2 * t] = acc[nb][0];
+      red[(warp * ROWS + g) * RED_M + nb * 8 + 2 * t + 1] = acc[nb][1];
+      if (ROWS == 16) {
+        red[(warp * ROWS + g + 8) * RED_M + nb * 8 + 2 * t] = acc[nb][2];
+        red[(warp * ROWS + g + 8) * RED_M + nb * 8 + 2 * t + 1] = acc[nb][3];
+      }
+    }
+    consumer_sync();
+    if (mode == 0) {
+      for (int i = threadIdx.x; i < ROWS * NB * 8; i += CW * 32) {
+        const int m = i / ROWS, r = i - m * ROWS;
+        if (m >= M || n0 + r >= N) continue;
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < CW; w++) sum += red[(w * ROWS + r) * RED_M + m];
+        out[(long long)m * N + n0 + r] = from_f32<OutT>(sum);
+      }
+    } else {
+      constexpr int HALF = ROWS / 2;       // rows 0..7 of a tile are gate rows, 8..15 the matching up rows
+      for (int i = threadIdx.x; i < HALF * NB * 8; i += CW * 32) {
+        const int m = i / HALF, r = i - m * HALF;
+        if (m >= M || n0 + r + HALF >= N) continue;
+        float gs = 0.f, us = 0.f;
+#pragma unroll
+        for (int w = 0; w < CW; w++) {
+          gs += red[(w * ROWS + r) * RED_M + m];
+          us += red[(w * ROWS + r + HALF) * RED_M + m];
+        }
+        out[(long long)m * (N / 2) + tile * HALF + r] = from_f32<OutT>(gs / (1.0f + expf(-gs)) * us);
+      }
+    }
+    consumer_sync();       // `red` is free for the next tile
+  }
+}
+
+template <int NB, int ROWS, typename OutT>
+int launch_tmap(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int mode, int* status,
+                int n_sms, cudaStream_t stream) {
+  const size_t smem = 1024 + (size_t)T_STAGES * T_STAGE_BYTES + 2 * T_STAGES * 8 + (size_t)CW * ROWS * (NB * 8 + 1) * 4;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(stream_tmap_kernel<NB, ROWS, OutT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  CUtensorMap map;
+  const int rc = tma_host::bf16_map_chunked(W, N, K, ROWS, 128 / ROWS, &map);
+  if (rc != 0) return rc;
+  const int n_tiles = (N + ROWS - 1) / ROWS;
+  const int grid = n_tiles < 2 * n_sms ? n_tiles : 2 * n_sms;
+  return (int)launch_dep(stream_tmap_kernel<NB, ROWS, OutT>, dim3(grid), dim3((CW + 1) * 32), smem, stream, x, map,
+                         out, M, N, K, mode, status);
+}
+
 template <int NB, int ROWS, typename OutT>
 int launch_one(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int mode, int* status,
                int n_sms, cudaStream_t stream) {
@@ -239,6 +406,20 @@ int dispatch(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, i
   }
   // few output rows: tiles of 8 rows, so that there are blocks for every SM
   const bool small = mode == 0 && (N + 15) / 16 < 2 * n_sms;
+  // Tensor copies only where every box lies inside the matrix along K (a whole number of
+  // stages): with K = 64, where boxes hang over the end of K, a stage was seen to be handed
+  // over before its rows had all arrived.  Rows past N are filled with zeros by the engine.
+  if (K % (small ? 1024 : 512) == 0 && g_stream_tensor_copies) {
+    if (M <= 8) {
+      return small ? launch_tmap<1, 8, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream)
+                   : launch_tmap<1, 16, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
+    }
+    if (M <= 16) {
+      return small ? launch_tmap<2, 8, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream)
+                   : launch_tmap<2, 16, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
+    }
+    return MF_ERR_BAD_ARG;
+  }
   if (M <= 8) {
     return small ? launch_one<1, 8, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream)
                  : launch_one<1, 16, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
@@ -253,6 +434,13 @@ int dispatch(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, i
 }  // namespace
 
 MF_API int mf_stream_max_rows() { return 16; }
+
+// 1 (the default): widths that are a multiple of 64 stream with one tensor copy per stage;
+// 0: every width streams with row-segment copies.  For tests and measurements.
+MF_API int mf_set_stream_tensor_copies(int on) {
+  g_stream_tensor_copies = on ? 1 : 0;
+  return 0;
+}
 
 // Arguments as mf_skinny_linear, plus `status`: a device int (may be null) that receives a
 // non-zero code if a wait inside the kernel ran out (1: producer, 2: consumer).

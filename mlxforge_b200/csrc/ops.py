@@ -170,9 +170,18 @@ def stream_max_rows() -> int:
     return int(library().mf_stream_max_rows())
 
 
+def set_stream_tensor_copies(on: bool) -> None:
+    """Whether ``stream_linear`` brings a stage with one tensor copy (widths that are a multiple
+    of 64; the default) or always with one copy per row segment."""
+    check(library().mf_set_stream_tensor_copies(1 if on else 0), "set_stream_tensor_copies", launches=0)
+
+
 def stream_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
     """The few-row product with weights streamed by bulk copies (see gemv_stream.cu);
-    same operands and results as ``skinny_linear``, at most ``stream_max_rows()`` rows."""
+    same operands and results as ``skinny_linear``, at most ``stream_max_rows()`` rows.
+    The kernel starts fetching ``w`` before it waits for the kernel launched before it, so
+    ``w`` must not be the output of that kernel (the engine's weights are written once, at
+    load time)."""
     _need_cuda(x, w, out)
     M, K = x.shape
     N = w.shape[0]

@@ -70,4 +70,35 @@ inline int bf16_map(const void* ptr, long long rows, long long cols, int box_row
   return 0;
 }
 
+// The same matrix seen as [cols/64 chunks][rows][64 elements]: a box of box_chunks x box_rows
+// spans of 128 bytes brings box_rows rows of 64 * box_chunks consecutive columns with ONE
+// copy, laid out in shared memory chunk by chunk ([chunk][row][128 bytes], 128-byte swizzle).
+// cols must be a multiple of 64.  0 on success.
+inline int bf16_map_chunked(const void* ptr, long long rows, long long cols, int box_rows, int box_chunks,
+                            CUtensorMap* out) {
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  static std::mutex mu;
+  if (cols % 64) return MF_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lock(mu);
+  const Key key{ptr, rows, cols, box_rows, box_chunks};
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  EncodeTiled enc = encoder();
+  if (!enc) return MF_ERR_BAD_ARG;
+  const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
+  const cuuint64_t strides[2] = {(cuuint64_t)cols * 2, 128};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_chunks};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return 20000 + (int)r;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
 }  // namespace tma_host

@@ -325,17 +325,31 @@ def test_rope_kv_write(dtype, nh, nkv, hd, rot):
 # ----------------------------------------------------------------------------- few-row products
 
 @pytest.mark.parametrize("M,N,K", [(1, 304, 80), (8, 2048, 2048), (5, 307, 136), (16, 96, 200), (9, 1000, 64),
-                                   (3, 128256, 64), (8, 16, 8192), (2, 5000, 520), (7, 40, 1032), (16, 4737, 1536)])
+                                   (3, 128256, 64), (8, 16, 8192), (2, 5000, 520), (7, 40, 1032), (16, 4737, 1536),
+                                   (3, 9000, 512), (11, 4744, 1024), (8, 300, 3072)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
-def test_stream_linear(M, N, K, out_dtype):
-    """The bulk-copy version: tiles that end inside a stage, K tails, more tiles than blocks."""
+@pytest.mark.parametrize("tensor_copies", [True, False])
+def test_stream_linear(M, N, K, out_dtype, tensor_copies):
+    """The bulk-copy version: tiles that end inside a stage, K tails, more tiles than blocks;
+    with one tensor copy per stage (widths of whole stages) and with a copy per row segment."""
+    from mlxforge_b200.csrc import ops
+    ops.set_stream_tensor_copies(tensor_copies)
+    try:
+        _check_stream_linear(M, N, K, out_dtype)
+    finally:
+        ops.set_stream_tensor_copies(True)
+
+
+def _check_stream_linear(M, N, K, out_dtype):
     import torch
     from mlxforge_b200.csrc import ops
     rng = np.random.default_rng(M * 1000 + N)
     x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
     w = bf16_round(rng.standard_normal((N, K)).astype(np.float32))
     out = torch.full((M, N), float("nan"), dtype=torch_dtype(out_dtype), device="cuda")
-    ops.stream_linear(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out)
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    torch.cuda.synchronize()      # the kernel fetches W before it waits for the kernel before it: W must be there
+    ops.stream_linear(xd, wd, out)
     ops.check_kernel_status()
     want = x.astype(np.float64) @ w.astype(np.float64).T
     tol = 3e-6 * np.sqrt(K) * 4 if out_dtype == "float32" else 2.0 ** -8 * np.abs(want).max() + 1e-3
@@ -350,7 +364,9 @@ def test_stream_linear(M, N, K, out_dtype):
         wg, wu = w[:I] * 0.2, w[I:] * 0.2
         gu = bf16_round(np.stack([wg.reshape(I // 8, 8, K), wu.reshape(I // 8, 8, K)], axis=1).reshape(N, K))
         act = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device="cuda")
-        ops.stream_linear(dev(x, torch.bfloat16), dev(gu, torch.bfloat16), act, swiglu=True)
+        gud = dev(gu, torch.bfloat16)
+        torch.cuda.synchronize()
+        ops.stream_linear(xd, gud, act, swiglu=True)
         gg = x.astype(np.float64) @ bf16_round(wg).astype(np.float64).T
         uu = x.astype(np.float64) @ bf16_round(wu).astype(np.float64).T
         want = gg / (1 + np.exp(-gg)) * uu
