@@ -290,16 +290,32 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
   const int t = blockIdx.x, h = blockIdx.y;
   const int pos = positions[t];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int s0 = lo / split_keys, s1 = pos / split_keys;
-  const long long row = ((long long)t * n_heads + h) * max_splits;
+  const int s0 = lo / split_keys, s1 = pos / split_keys, n = s1 - s0 + 1;
+  const long long row = ((long long)t * n_heads + h) * max_splits + s0;
+  // every warp works out the same weights, a split per lane: w_s = 2^(m_s - M) / L, so that the
+  // loads of the splits' statistics go out together and not one after the other
+  const int lane = threadIdx.x & 31;
   float M = -INFINITY;
-  for (int s = s0; s <= s1; s++) M = fmaxf(M, part_ml[(row + s) * 2]);
+  for (int s = lane; s < n; s += 32) M = fmaxf(M, part_ml[(row + s) * 2]);
+  M = warp_max(M);
   float L = 0.f;
-  for (int s = s0; s <= s1; s++) L += part_ml[(row + s) * 2 + 1] * exp2f(part_ml[(row + s) * 2] - M);
+  for (int s = lane; s < n; s += 32) L += part_ml[(row + s) * 2 + 1] * exp2f(part_ml[(row + s) * 2] - M);
+  L = warp_sum(L);
   const float inv = 1.0f / L;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.f;
-    for (int s = s0; s <= s1; s++) acc += part_o[(row + s) * hd + d] * exp2f(part_ml[(row + s) * 2] - M);
+    int s = 0;
+    for (; s + 4 <= n; s += 4) {
+      const float o0 = part_o[(row + s) * hd + d], o1 = part_o[(row + s + 1) * hd + d];
+      const float o2 = part_o[(row + s + 2) * hd + d], o3 = part_o[(row + s + 3) * hd + d];
+      const float m0 = part_ml[(row + s) * 2], m1 = part_ml[(row + s + 1) * 2];
+      const float m2 = part_ml[(row + s + 2) * 2], m3 = part_ml[(row + s + 3) * 2];
+      acc += o0 * exp2f(m0 - M);
+      acc += o1 * exp2f(m1 - M);
+      acc += o2 * exp2f(m2 - M);
+      acc += o3 * exp2f(m3 - M);
+    }
+    for (; s < n; s++) acc += part_o[(row + s) * hd + d] * exp2f(part_ml[(row + s) * 2] - M);
     out[((long long)t * n_heads + h) * hd + d] = __float2bfloat16_rn(acc * inv);
   }
 }
