@@ -220,7 +220,7 @@ stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
 // the fragment reads off each other's banks: a thread takes the 16-byte pieces 2t and 2t+1 of
 // its warp's chunk, so the eight threads of a quarter-warp (rows g, g+1) touch eight different
 // pieces.  Needs K to be a whole number of stages; other widths take the kernel above.
-constexpr int T_STAGES = 3;
+constexpr int T_STAGES = 4;
 constexpr int T_STAGE_BYTES = 16384;
 
 __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, int c0, int c1, int c2,
