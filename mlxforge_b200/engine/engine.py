@@ -53,6 +53,7 @@ class EngineConfig:
     prefill_chunk: int = 512
     skinny_mm: bool = True             # few-row products by the skinny kernel
     cuda_graphs: bool = True           # replay decode-only steps from captured graphs
+    pipeline: bool = True              # launch a decode step before the host has the tokens of the one before
     gemm: str = ""                     # many-row products: "library" | "tcgen05" ("" = MLXFORGE_GEMM or library)
     rope_scaling: str = ""             # JSON object replacing the checkpoint's rope_scaling
 
@@ -104,6 +105,10 @@ class Engine:
         self._thread: Optional[threading.Thread] = None
         self._stop = False
         self._t_busy = 0.0
+        # a launched step whose sampled tokens have not been collected: (entries, sampler handle)
+        self._inflight = None
+        self.pipeline = bool(config.pipeline)
+        self.steps_ahead = 0              # steps launched before the tokens of the step before were known
         self._device_index = rt.device.index if rt.device.index is not None else torch.cuda.current_device()
 
     # ------------------------------------------------------------------ submit
@@ -129,9 +134,59 @@ class Engine:
         return req
 
     # ------------------------------------------------------------------ the loop
+    @property
+    def idle(self) -> bool:
+        """Nothing waiting, nothing running and no step on its way."""
+        return self.scheduler.idle and self._inflight is None
+
     def step(self) -> int:
-        """One iteration: plan, run, sample, commit.  Returns the number of tokens
-        the step ran (0 when there was nothing to do)."""
+        """One iteration.  Returns the number of tokens it ran or committed (0 when there was
+        nothing to do).
+
+        A step is launched without waiting for it: its sampled tokens are collected by the
+        NEXT call.  While every running request is decoding, that next call first launches the
+        step after (its tokens are fed on the device from what the step on its way samples,
+        ``Scheduler.continue_decoding`` says when that is sound) and only then collects, so the
+        device goes from one step into the next while the host emits tokens and does its
+        bookkeeping.  A request that ends with a token collected this way has a row in the step
+        already launched; that row's result is dropped.  Requests with penalties need their
+        history on the host before they sample: their steps are collected at once."""
+        inflight = self._inflight
+        if inflight is None:
+            return self._launch_planned()
+        entries, handle = inflight
+        t0 = time.perf_counter()
+        nxt, nxt_handle = None, None
+        if self.pipeline:
+            with self._lock:
+                nxt = self.scheduler.continue_decoding(entries)
+        try:
+            if nxt is not None:
+                try:
+                    step_entries = [StepEntry(e.request.seq, [0], [0]) for e in nxt]
+                    logits = self.runner.step(step_entries, device_tokens=self.sampler.device_ids)
+                except OutOfPages:
+                    nxt = None
+                else:
+                    rows = [e.request for e in nxt]
+                    nxt_handle = self.sampler.launch(logits, [r.params for r in rows],
+                                                     [len(r.output_ids) + 1 for r in rows])
+                    self.steps_ahead += 1
+            sampled = self.sampler.collect(handle)
+        except Exception as exc:
+            self._inflight = None
+            with self._lock:
+                self.scheduler.fail_all(f"{type(exc).__name__}: {exc}")
+            raise
+        with self._lock:
+            self.scheduler.commit(entries, sampled)
+        self._inflight = (nxt, nxt_handle) if nxt is not None else None
+        self._t_busy += time.perf_counter() - t0
+        return sum(e.count for e in entries)
+
+    def _launch_planned(self) -> int:
+        """Plan a step with the scheduler and launch it.  Its tokens are collected by the next
+        call of ``step`` unless a request's penalties need them on the host first."""
         with self._lock:
             entries = self.scheduler.plan()
         if not entries:
@@ -143,12 +198,16 @@ class Engine:
                 ids = e.request.tokens(e.start, e.count)
                 step_entries.append(StepEntry(e.request.seq, ids, [e.count - 1] if e.samples else []))
             logits = self.runner.step(step_entries)
-            sampled: List[int] = []
+            rows = [e.request for e in entries if e.samples]
+            handle = None
             if logits is not None:
-                rows = [e.request for e in entries if e.samples]
-                sampled = self.sampler.sample(logits, [r.params for r in rows],
-                                              [len(r.output_ids) for r in rows],
-                                              [r.all_ids if r.params.has_penalties else () for r in rows])
+                handle = self.sampler.launch(logits, [r.params for r in rows], [len(r.output_ids) for r in rows],
+                                             [r.all_ids if r.params.has_penalties else () for r in rows])
+            if self.pipeline and not any(r.params.has_penalties for r in rows):
+                self._inflight = (entries, handle)
+                self._t_busy += time.perf_counter() - t0
+                return sum(e.count for e in entries)
+            sampled = self.sampler.collect(handle)
         except Exception as exc:    # the step failed: no request can go on
             with self._lock:
                 self.scheduler.fail_all(f"{type(exc).__name__}: {exc}")
@@ -159,8 +218,8 @@ class Engine:
         return sum(e.count for e in entries)
 
     def run_until_idle(self) -> None:
-        while not self.scheduler.idle:
-            if self.step() == 0 and not self.scheduler.idle:
+        while not self.idle:
+            if self.step() == 0 and not self.idle:
                 raise RuntimeError("scheduler made no progress with requests outstanding")
 
     # ------------------------------------------------------------------ worker thread
@@ -176,9 +235,9 @@ class Engine:
             torch.cuda.set_device(self._device_index)
             while True:
                 with self._wake:
-                    while self.scheduler.idle and not self._stop:
+                    while self.idle and not self._stop:
                         self._wake.wait(timeout=0.1)
-                    if self._stop and self.scheduler.idle:
+                    if self._stop and self.idle:
                         return
                 try:
                     self.step()
@@ -228,5 +287,5 @@ class Engine:
             "running": len(self.scheduler.running), "waiting": len(self.scheduler.waiting),
             "pages_free": min(self.cache.free_pages()) if self.cache.pools else 0,
             "pages_total": min(self.cache.total_pages()) if self.cache.pools else 0,
-            "busy_seconds": self._t_busy,
+            "busy_seconds": self._t_busy, "steps_ahead": self.steps_ahead,
         }

@@ -216,6 +216,32 @@ class Scheduler:
             r.seq = None
             self._finish(r, FINISH_CANCEL)
 
+    def continue_decoding(self, entries: List[PlannedEntry]) -> Optional[List[PlannedEntry]]:
+        """``entries`` is a step that has been launched but not committed.  If the step after it
+        is bound to be the same requests with one more token each, whatever the launched step
+        samples short of an end-of-sequence token (every running request is in it and decoding,
+        nobody waits, nobody is cancelled or would reach its length with the token on its way,
+        and the pages are there), return that step; else None.  A request that does end with the
+        token on its way leaves a row in the returned step whose result ``commit`` drops."""
+        if self.waiting or len(entries) != len(self.running):
+            return None
+        n_groups = len(self.cache.free_pages())
+        taken = [0] * n_groups
+        nxt: List[PlannedEntry] = []
+        for e, r in zip(entries, self.running):
+            if e.request is not r or e.count != 1 or not e.samples or r.cancelled or r.finished:
+                return None
+            if not r.output_ids or len(r.output_ids) + 2 > r.max_tokens:
+                return None
+            need = self.cache.pages_needed(r.seq, 1)
+            if not self._pages_fit(taken, need):
+                return None
+            taken = [a + b for a, b in zip(taken, need)]
+            nxt.append(PlannedEntry(r, e.start + 1, 1, True))
+        if len(nxt) > self.cfg.token_budget:
+            return None
+        return nxt
+
     # ------------------------------------------------------------------ after the step
     def commit(self, entries: List[PlannedEntry], sampled: List[int]) -> None:
         """``sampled`` holds one token for every entry with ``samples`` set, in order."""
@@ -223,6 +249,10 @@ class Scheduler:
         self.metrics.steps += 1
         for e in entries:
             r = e.request
+            if r.finished:                 # ended while this step was on its way: its row is dropped
+                if e.samples:
+                    next(it)
+                continue
             r.computed += e.count
             if e.count == 1 and r.output_ids and e.start >= len(r.prompt_ids):
                 self.metrics.decode_tokens += 1

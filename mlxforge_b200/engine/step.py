@@ -96,14 +96,22 @@ class ModelRunner:
         self.graph_replays = 0
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None
+             ) -> Optional[torch.Tensor]:
         """Run the entries as one batch.  Returns float32 logits ``[wanted, vocab]``
         on the device in the order of the entries and of their ``want`` lists
         (None if nothing is wanted).  The returned tensor is scratch that the
-        next step overwrites.  On ``OutOfPages`` nothing has changed."""
+        next step overwrites.  On ``OutOfPages`` nothing has changed.
+
+        ``device_tokens`` (int32, one per entry): the step's tokens are taken from there, on
+        the device, in the order of the entries, and the entries' own token ids are ignored;
+        every entry must then bring exactly one token.  This is how a step is launched
+        before the host has seen what the step before it sampled."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return None
+        if device_tokens is not None and any(len(e.tokens) != 1 for e in entries):
+            raise ValueError("device_tokens: every entry must bring exactly one token")
         seen = set()
         for e in entries:
             if e.seq.closed:
@@ -115,13 +123,16 @@ class ModelRunner:
             for w in e.want:
                 if not (0 <= w < n):
                     raise IndexError(f"want index {w} is outside the {n} tokens of its entry")
-            lo, hi = min(e.tokens), max(e.tokens)
+            lo, hi = (0, 0) if device_tokens is not None else (min(e.tokens), max(e.tokens))
             if lo < 0 or hi >= self.vocab:
                 raise IndexError(f"token id {lo if lo < 0 else hi} is outside the vocabulary [0, {self.vocab})")
         self.cache.reserve([(e.seq, len(e.tokens)) for e in entries])
         graphed = self.cuda_graphs and all(len(e.tokens) == 1 for e in entries)
         decode_only = all(len(e.tokens) == 1 for e in entries)
         batch = self._build(entries, pad_tables=decode_only)
+        if device_tokens is not None:
+            # after the copy of the metadata, in stream order: one-token entries keep their order
+            batch.tokens.copy_(device_tokens[:len(entries)], non_blocking=True)
         logits = self._forward_graphed(batch) if graphed else self.model.forward(batch, self.cache)
         for e in entries:
             self.cache.commit(e.seq, len(e.tokens))

@@ -33,16 +33,38 @@ class Sampler:
         self._host = torch.empty((2, self._cap), dtype=torch.float32, pin_memory=True)
         self._dev = torch.empty((2, self._cap), dtype=torch.float32, device=self.device)
         self._out = torch.empty(self._cap, dtype=torch.int32, device=self.device)
-        self._out_host = torch.empty(self._cap, dtype=torch.int32, pin_memory=True)
+        # two host buffers taken in turn: one launch may be in flight while the one before is read
+        self._out_host = [torch.empty(self._cap, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._events = [torch.cuda.Event() for _ in range(2)]
+        self._turn = 0
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], indices: Sequence[int],
                histories: Sequence[Sequence[int]] = ()) -> List[int]:
         """One token for every row of ``logits`` [n, V] (float32, device).
         ``indices[r]`` is the output index of row r's request (it selects the
         draw); ``histories[r]`` the tokens its penalties look at."""
+        return self.collect(self.launch(logits, params, indices, histories))
+
+    @property
+    def device_ids(self) -> torch.Tensor:
+        """Where the last launch writes its tokens on the device (int32, a row each)."""
+        return self._out
+
+    def collect(self, handle) -> List[int]:
+        """Wait for a launch and return its tokens."""
+        if handle is None:
+            return []
+        turn, n = handle
+        self._events[turn].synchronize()
+        return self._out_host[turn][:n].tolist()
+
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], indices: Sequence[int],
+               histories: Sequence[Sequence[int]] = ()):
+        """Start the sampling of every row and the copy of the tokens to the host; nothing
+        waits.  The handle goes to ``collect``; at most two launches may be uncollected."""
         n = logits.shape[0]
         if n == 0:
-            return []
+            return None
         self._ensure(n)
         if any(p.has_penalties for p in params):
             ops.apply_penalties(logits, params, histories)
@@ -59,6 +81,8 @@ class Sampler:
             if any(p.has_filters and not p.greedy for p in params):
                 ops.filter_logits(logits, params)
             ops.sample(logits, self._dev[0, :n], self._dev[1, :n], out)
-        self._out_host[:n].copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._out_host[:n].tolist()
+        turn = self._turn
+        self._turn ^= 1
+        self._out_host[turn][:n].copy_(out, non_blocking=True)
+        self._events[turn].record()
+        return (turn, n)

@@ -5,6 +5,8 @@ cancelling, what happens when pages run out).  CPU only: the scheduler is driven
 with a fake step that returns chosen tokens."""
 import random
 
+import numpy as np
+
 import pytest
 import torch
 
@@ -300,3 +302,123 @@ def test_random_load_every_request_gets_its_own_stream(seed):
         if r.finish_reason == "length":
             assert len(r.output_ids) == r.max_tokens
     assert m.free_pages() == m.total_pages() and m.slots.n_free == m.slots.n_slots
+
+
+# ----------------------------------------------------------------------------- steps launched ahead
+
+class PipelinedFakeEngine(FakeEngine):
+    """Drives a Scheduler the way the pipelined Engine.step does: a step is launched (the cache
+    reserved and advanced) and its tokens are only known at the next call, which, when
+    ``continue_decoding`` allows it, launches the step after before it commits."""
+
+    def __init__(self, sched, cache, next_token):
+        super().__init__(sched, cache, next_token)
+        self.inflight = None
+        self.ahead = 0
+
+    def _launch(self, entries):
+        self.cache.reserve([(e.request.seq, e.count) for e in entries])
+        for e in entries:
+            assert e.start == e.request.seq.length, "portions of one request must run in order, once"
+            self.cache.commit(e.request.seq, e.count)
+        self.log.append([(e.request.request_id, e.start, e.count, e.samples) for e in entries])
+
+    def step(self):
+        if self.inflight is None:
+            entries = self.s.plan()
+            if not entries:
+                return 0
+            self._launch(entries)
+            self.inflight = entries
+            return sum(e.count for e in entries)
+        entries = self.inflight
+        nxt = self.s.continue_decoding(entries)
+        if nxt is not None:
+            self._launch(nxt)          # before the tokens of `entries` are known
+            self.ahead += 1
+        sampled = [self.next_token(e.request, e.start + e.count) for e in entries if e.samples]
+        self.s.commit(entries, sampled)
+        self.cache.check()
+        self.inflight = nxt
+        return sum(e.count for e in entries)
+
+    def run(self, limit=10000):
+        n = 0
+        while not (self.s.idle and self.inflight is None):
+            assert self.step() > 0 or (self.s.idle and self.inflight is None), "no progress"
+            n += 1
+            assert n < limit
+        return n
+
+
+def test_continue_decoding_says_when_the_next_step_is_known():
+    s, m, _ = make(token_budget=64, prefill_chunk=32, max_running=4)
+    eng = PipelinedFakeEngine(s, m, tok)
+    a = Request([1] * 10, GREEDY, max_tokens=6)
+    b = Request([2] * 5, GREEDY, max_tokens=50)
+    s.submit(a), s.submit(b)
+    eng.step()                                   # both prompts, launched
+    assert s.continue_decoding(eng.inflight) is None, "a prompt portion is on its way: not a decode step"
+    eng.step()                                   # commit: both have their first token
+    eng.step()                                   # a decode step launched
+    nxt = s.continue_decoding(eng.inflight)
+    assert [(e.request.request_id, e.start, e.count, e.samples) for e in nxt] == \
+        [(a.request_id, 11, 1, True), (b.request_id, 6, 1, True)]
+    c = Request([3] * 4, GREEDY, max_tokens=3)
+    s.submit(c)
+    assert s.continue_decoding(eng.inflight) is None, "somebody waits: the next step has to be planned"
+    eng.run()
+    assert a.output_ids == [tok(a, 10 + i) for i in range(6)] and a.finish_reason == "length"
+    assert len(b.output_ids) == 50 and len(c.output_ids) == 3
+    assert eng.ahead > 20, "steady decoding was launched ahead"
+    # the step in which a got its last token was not followed by one with a in it
+    last_a = max(i for i, st in enumerate(eng.log) if any(x[0] == a.request_id for x in st))
+    assert eng.log[last_a][[x[0] for x in eng.log[last_a]].index(a.request_id)][1] == 10 + 4
+    assert m.free_pages() == m.total_pages()
+
+
+def test_a_request_that_ends_while_a_step_is_ahead_leaves_a_dropped_row():
+    s, m, _ = make(max_running=4)
+    eng = PipelinedFakeEngine(s, m, tok)
+    a = Request([3, 4, 5], GREEDY, max_tokens=40)
+    b = Request([6, 7], GREEDY, max_tokens=40)
+    a.eos_ids = (tok(a, 8),)                     # a's sixth token is EOS: nobody can know before it is sampled
+    s.submit(a), s.submit(b)
+    eng.run()
+    assert a.finish_reason == "stop" and a.output_ids == [tok(a, 3 + i) for i in range(5)]
+    assert b.finish_reason == "length" and b.output_ids == [tok(b, 2 + i) for i in range(40)]
+    rows_of_a = [x for st in eng.log for x in st if x[0] == a.request_id]
+    assert rows_of_a[-1][1] == 3 + 5, "one row of a ran past its end (launched before the EOS was seen)"
+    assert m.free_pages() == m.total_pages() and m.slots.n_free == 4
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_pipelined_random_load_matches_the_plain_loop(seed):
+    """Random arrivals, lengths, EOS tokens and cancels, few pages: launching ahead changes no
+    request's tokens or finish reason, and no page is lost."""
+    results = []
+    for cls in (FakeEngine, PipelinedFakeEngine):
+        rng = np.random.default_rng(seed)
+        s, m, _ = make(max_tokens=int(rng.integers(200, 600)), token_budget=48, prefill_chunk=16, max_running=4)
+        eng = cls(s, m, lambda r, n: (r.tag * 7 + n) % 13 + 1)
+        reqs = []
+        for i in range(14):
+            r = Request([int(x) for x in rng.integers(1, 50, size=int(rng.integers(1, 60)))], GREEDY,
+                        max_tokens=int(rng.integers(1, 40)))
+            r.tag = i
+            if rng.random() < 0.5:
+                r.eos_ids = (int(rng.integers(1, 14)),)
+            reqs.append(r)
+        pending = list(reqs)
+        n = 0
+        while pending or not s.idle or getattr(eng, "inflight", None) is not None:
+            while pending and rng.random() < 0.4:
+                assert s.submit(pending.pop(0))
+            if eng.step() == 0 and pending:
+                assert s.submit(pending.pop(0))
+            n += 1
+            assert n < 5000
+        m.check()
+        assert m.free_pages() == m.total_pages()
+        results.append([(r.output_ids, r.finish_reason) for r in reqs])
+    assert results[0] == results[1]

@@ -240,3 +240,35 @@ def test_dependent_launch_and_graphs_change_no_bit(tiny):
     fast, n1 = run(True, True)
     assert n0 == 0 and n1 >= 4, "the second run must have replayed graphs"
     assert torch.equal(eager, fast)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_change_no_token(tiny, dtype):
+    """Decode steps launched before the host has the tokens of the step before (fed on the
+    device) give every request the tokens it gets from the step-by-step loop: greedy and
+    seeded temperature sampling, requests of different lengths, one that meets its EOS."""
+    import mlxforge_b200 as mf
+    d, cfg, w = tiny["B"]
+    prompts = [random_prompt(cfg, n, 200 + i) for i, n in enumerate([12, 45, 3, 70])]
+    lengths = [40, 25, 33, 40]
+
+    def run(pipeline, params):
+        eng = _engine(d, dtype=dtype, pipeline=pipeline)
+        reqs = [eng.submit_ids(p, params, n, eos_ids=[]) for p, n in zip(prompts, lengths)]
+        eng.run_until_idle()
+        outs = [list(r.output_ids) for r in reqs]
+        # again, now with the 10th token of the first request as its EOS
+        eng2 = _engine(d, dtype=dtype, pipeline=pipeline)
+        reqs2 = [eng2.submit_ids(p, params, n, eos_ids=([outs[0][9]] if i == 0 else []))
+                 for i, (p, n) in enumerate(zip(prompts, lengths))]
+        eng2.run_until_idle()
+        m = eng2.metrics()
+        assert m["pages_free"] == m["pages_total"]
+        return outs, [(list(r.output_ids), r.finish_reason) for r in reqs2], eng.steps_ahead
+
+    for params in (mf.GREEDY, mf.SamplingParams(temperature=0.9, top_k=20, seed=5)):
+        plain, plain_eos, n0 = run(False, params)
+        ahead, ahead_eos, n1 = run(True, params)
+        assert n0 == 0 and n1 >= 20, "the second run must have launched steps ahead"
+        assert ahead == plain and ahead_eos == plain_eos
+        assert plain_eos[0][1] == "stop" and len(plain_eos[0][0]) <= 9
