@@ -220,7 +220,8 @@ stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
 // the fragment reads off each other's banks: a thread takes the 16-byte pieces 2t and 2t+1 of
 // its warp's chunk, so the eight threads of a quarter-warp (rows g, g+1) touch eight different
 // pieces.  Needs K to be a whole number of stages; other widths take the kernel above.
-constexpr int T_STAGES = 4;
+// Stages of the ring: four, or six where a product has so few tiles that its blocks do not fill
+// the device and each has to keep more on its way.
 constexpr int T_STAGE_BYTES = 16384;
 
 __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, int c0, int c1, int c2,
@@ -230,7 +231,7 @@ __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
-template <int NB, int ROWS, typename OutT>
+template <int NB, int ROWS, int T_STAGES, typename OutT>
 __global__ void __launch_bounds__((CW + 1) * 32)
 stream_tmap_kernel(const __nv_bfloat16* __restrict__ x, const __grid_constant__ CUtensorMap map,
                    OutT* __restrict__ out, int M, int N, int K, int mode, int* __restrict__ status) {
@@ -355,13 +356,13 @@ stream_tmap_kernel(const __nv_bfloat16* __restrict__ x, const __grid_constant__ 
   }
 }
 
-template <int NB, int ROWS, typename OutT>
+template <int NB, int ROWS, int T_STAGES, typename OutT>
 int launch_tmap(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int mode, int* status,
                 int n_sms, cudaStream_t stream) {
   const size_t smem = 1024 + (size_t)T_STAGES * T_STAGE_BYTES + 2 * T_STAGES * 8 + (size_t)CW * ROWS * (NB * 8 + 1) * 4;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(stream_tmap_kernel<NB, ROWS, OutT>,
+    cudaError_t e = cudaFuncSetAttribute(stream_tmap_kernel<NB, ROWS, T_STAGES, OutT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -371,7 +372,7 @@ int launch_tmap(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M
   if (rc != 0) return rc;
   const int n_tiles = (N + ROWS - 1) / ROWS;
   const int grid = n_tiles < 2 * n_sms ? n_tiles : 2 * n_sms;
-  return (int)launch_dep(stream_tmap_kernel<NB, ROWS, OutT>, dim3(grid), dim3((CW + 1) * 32), smem, stream, x, map,
+  return (int)launch_dep(stream_tmap_kernel<NB, ROWS, T_STAGES, OutT>, dim3(grid), dim3((CW + 1) * 32), smem, stream, x, map,
                          out, M, N, K, mode, status);
 }
 
@@ -410,13 +411,18 @@ int dispatch(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, i
   // stages): with K = 64, where boxes hang over the end of K, a stage was seen to be handed
   // over before its rows had all arrived.  Rows past N are filled with zeros by the engine.
   if (K % (small ? 1024 : 512) == 0 && g_stream_tensor_copies) {
+    // few tiles of many stages each: the blocks do not fill the device, so each keeps six stages on
+    // their way instead of four
+    const bool deep = small && (N + 7) / 8 <= 2 * n_sms && K >= 6 * 1024;
     if (M <= 8) {
-      return small ? launch_tmap<1, 8, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream)
-                   : launch_tmap<1, 16, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
+      if (deep) return launch_tmap<1, 8, 6, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
+      return small ? launch_tmap<1, 8, 4, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream)
+                   : launch_tmap<1, 16, 4, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
     }
     if (M <= 16) {
-      return small ? launch_tmap<2, 8, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream)
-                   : launch_tmap<2, 16, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
+      if (deep) return launch_tmap<2, 8, 6, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
+      return small ? launch_tmap<2, 8, 4, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream)
+                   : launch_tmap<2, 16, 4, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
     }
     return MF_ERR_BAD_ARG;
   }
