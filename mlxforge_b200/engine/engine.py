@@ -54,7 +54,7 @@ class EngineConfig:
     skinny_mm: bool = True             # few-row products by the skinny kernel
     cuda_graphs: bool = True           # replay decode-only steps from captured graphs
     pipeline: bool = True              # launch a decode step before the host has the tokens of the one before
-    gemm: str = ""                     # many-row products: "library" | "tcgen05" ("" = MLXFORGE_GEMM or library)
+    gemm: str = ""                     # many-row products: "auto" | "library" | "tcgen05" ("" = MLXFORGE_GEMM or auto)
     rope_scaling: str = ""             # JSON object replacing the checkpoint's rope_scaling
 
     def validate(self) -> None:
@@ -86,8 +86,8 @@ class Engine:
         rt.skinny_enabled = bool(config.skinny_mm)
         rt.reserve_rows = config.token_budget
         if config.gemm:
-            if config.gemm not in ("library", "tcgen05"):
-                raise ValueError(f"EngineConfig: gemm must be 'library' or 'tcgen05', got '{config.gemm}'")
+            if config.gemm not in ("auto", "library", "tcgen05"):
+                raise ValueError(f"EngineConfig: gemm must be 'auto', 'library' or 'tcgen05', got '{config.gemm}'")
             rt.gemm_backend = config.gemm
         elt = 4 if dtype == torch.float32 else 2
         per_token = max(1, self.model.cache_layout.bytes_per_token(elt))

@@ -35,10 +35,15 @@ class Runtime:
         # rows at or below which the few-row product streams its weights by bulk copies
         self.stream_max_rows = 16
         # many-row bfloat16 products: "library" (cuBLAS through torch.mm, as the reference uses
-        # its library's matmul there) or "tcgen05" (this engine's own tensor-memory kernel)
-        self.gemm_backend = os.environ.get("MLXFORGE_GEMM", "library")
-        if self.gemm_backend not in ("library", "tcgen05"):
-            raise ValueError(f"MLXFORGE_GEMM must be 'library' or 'tcgen05', got '{self.gemm_backend}'")
+        # its library's matmul there), "tcgen05" (this engine's own tensor-memory kernel), or
+        # "auto": the own kernel where it has SwiGLU in its epilogue (gate|up: one kernel instead
+        # of the library's product and an elementwise pass over its result), the library elsewhere
+        self.gemm_backend = os.environ.get("MLXFORGE_GEMM", "auto")
+        if self.gemm_backend not in ("auto", "library", "tcgen05"):
+            raise ValueError(f"MLXFORGE_GEMM must be 'auto', 'library' or 'tcgen05', got '{self.gemm_backend}'")
+        # rows from which "auto" takes the own kernel for gate|up (below, the library's product
+        # of few rows and the elementwise pass are the shorter way)
+        self.fused_swiglu_min_rows = 256
 
     # ------------------------------------------------------------------ scratch
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -92,7 +97,9 @@ class Runtime:
         if group == 8 and w_gu.shape[0] % 16 == 0 and self._skinny(x, w_gu):
             (ops.stream_linear if x.shape[0] <= self.stream_max_rows else ops.skinny_linear)(x, w_gu, out, swiglu=True)
             return out
-        if self.gemm_backend == "tcgen05" and group == 8 and w_gu.shape[0] % 16 == 0 and ops.gemm_ok(x, w_gu):
+        own = self.gemm_backend == "tcgen05" or (self.gemm_backend == "auto"
+                                                 and x.shape[0] >= self.fused_swiglu_min_rows)
+        if own and group == 8 and w_gu.shape[0] % 16 == 0 and ops.gemm_ok(x, w_gu):
             ops.gemm_bf16(x, w_gu, out, swiglu=True)
             return out
         gu = self.linear(x, w_gu, self.buffer("ffn.gu", (x.shape[0], w_gu.shape[0])))
