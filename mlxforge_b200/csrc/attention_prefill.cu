@@ -303,15 +303,22 @@ int launch_prefill(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __
 
 }  // namespace
 
+int launch_prefill_tc(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
+                      __nv_bfloat16* out, const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len,
+                      int table_row0, int n_seqs, int max_q_len, int n_tokens, int n_heads, PagedView pv,
+                      float scale, int window, int* status, cudaStream_t stream);
+
 // q, out: [T, n_heads * hd] of the whole step.  The n_seqs sequences start at row
 // `table_row0` of the block table; seq_q_start / seq_q_len / seq_ctx_len are their
 // first token's index in q, their number of new tokens and their length after the
-// step.  `max_q_len` bounds seq_q_len (it sizes the grid).
+// step.  `max_q_len` bounds seq_q_len (it sizes the grid); `n_tokens` is T.  `status`: a device int
+// (may be null) for the bounded waits of the tcgen05 kernel (attention_prefill_tc.cu), which
+// takes head size 64 when a portion has at least 128 tokens.
 MF_API int mf_attention_prefill(const void* q, const void* k_pool, const void* v_pool, void* out,
                                 const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len,
-                                int table_row0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd,
-                                const int* block_table, int bt_stride, int page_size, float scale, int window,
-                                cudaStream_t stream) {
+                                int table_row0, int n_seqs, int max_q_len, int n_tokens, int n_heads, int n_kv,
+                                int hd, const int* block_table, int bt_stride, int page_size, float scale,
+                                int window, int* status, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return 0;
   if (hd < 16 || hd > 256 || hd % 16 || n_kv <= 0 || n_heads % n_kv) return MF_ERR_BAD_ARG;
   if (n_heads > 65535 || n_seqs > 65535) return MF_ERR_BAD_ARG;
@@ -319,6 +326,11 @@ MF_API int mf_attention_prefill(const void* q, const void* k_pool, const void* v
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_pool,
                       *vv = (const __nv_bfloat16*)v_pool;
   __nv_bfloat16* oo = (__nv_bfloat16*)out;
+  {
+    const int rc = launch_prefill_tc(qq, kk, vv, oo, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs,
+                                     max_q_len, n_tokens, n_heads, pv, scale, window, status, stream);
+    if (rc != MF_ERR_BAD_ARG) return rc;
+  }
   if (hd <= 64)
     return launch_prefill<64>(qq, kk, vv, oo, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs, max_q_len,
                               n_heads, pv, scale, window, stream);

@@ -113,9 +113,15 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
         raise KernelError("attention_prefill: bfloat16 only")
     check(library().mf_attention_prefill(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
                                          seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_ctx_len.data_ptr(),
-                                         table_row0, seq_q_len.shape[0], max_q_len, n_heads, n_kv, head_dim,
-                                         block_table.data_ptr(), block_table.shape[1], page_size, scale, window,
-                                         _stream()), "attention_prefill")
+                                         table_row0, seq_q_len.shape[0], max_q_len, q.shape[0], n_heads, n_kv,
+                                         head_dim, block_table.data_ptr(), block_table.shape[1], page_size, scale,
+                                         window, kernel_status(q.device).data_ptr(), _stream()), "attention_prefill")
+
+
+def set_prefill_tcgen05(on: bool) -> None:
+    """Whether portions of at least 128 tokens with head size 64 take the tcgen05 attention
+    kernel (the default) or every shape the mma.sync one."""
+    check(library().mf_set_prefill_tcgen05(1 if on else 0), "set_prefill_tcgen05", launches=0)
 
 
 def skinny_max_rows() -> int:

@@ -469,6 +469,53 @@ def test_attention_prefill(case):
             assert d < 1.5e-2, (s, j, pos, d)
 
 
+@pytest.mark.parametrize("nh,nkv,lengths,q_lens,window", [
+    (8, 2, [700, 130, 513], [700, 130, 300], 0),          # whole prompts and the tail of a longer context
+    (4, 4, [300, 640], [300, 200], 100),                  # a window shorter than a key tile
+    (4, 1, [128, 2000, 5], [128, 129, 2], 0),             # exactly one tile; one query past a tile; two tokens
+    (4, 2, [1500], [1100], 700),                          # a window over several key tiles
+    (32, 8, [2048], [2048], 0),
+])
+def test_attention_prefill_tcgen05(nh, nkv, lengths, q_lens, window):
+    """The tcgen05 kernel (head size 64, a portion of 128 tokens or more in the launch): every
+    row of every portion against the plain formula, unused pages and page tails full of NaN."""
+    import torch
+    from mlxforge_b200.csrc import ops
+    hd = 64
+    pc = Paged(lengths, nkv, hd, dtype="bfloat16", seed=len(lengths) + nh)
+    rng = np.random.default_rng(18)
+    starts = np.cumsum([3] + q_lens[:-1]).astype(np.int32)        # 3 unrelated rows come first
+    T = 3 + sum(q_lens) + 2                                        # and 2 after
+    q = bf16_round(rng.standard_normal((T, nh, hd)).astype(np.float32))
+    scale = hd ** -0.5
+    table = np.concatenate([np.full((1, pc.table.shape[1]), -1, dtype=np.int32), pc.table])
+    args = (dev(q.reshape(T, -1), torch.bfloat16), pc.k_pool, pc.v_pool)
+    meta = (dev(starts), dev(np.array(q_lens, dtype=np.int32)), dev(np.array(lengths, dtype=np.int32)), 1,
+            max(q_lens), dev(table), pc.page, nh, nkv, hd, scale, window)
+    outs = []
+    for tc in (True, False):
+        ops.set_prefill_tcgen05(tc)
+        try:
+            out = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ops.attention_prefill(*args, out, *meta)
+            ops.check_kernel_status()
+        finally:
+            ops.set_prefill_tcgen05(True)
+        outs.append(host(out).reshape(T, nh, hd))
+    got, other = outs
+    assert np.isnan(got[:3]).all() and np.isnan(got[-2:]).all(), "rows that belong to no portion are left alone"
+    step = 1 if sum(q_lens) <= 800 else 7                          # the plain formula is slow: every 7th row of long ones
+    for s, (n, ql) in enumerate(zip(lengths, q_lens)):
+        rows = sorted(set(range(0, ql, step)) | {0, ql - 1, min(ql - 1, 127), min(ql - 1, 128)})
+        for j in rows:
+            pos = n - ql + j
+            want = pc.reference(q[starts[s] + j], s, pos, scale, window)
+            d = np.max(np.abs(got[starts[s] + j] - want))
+            assert d < 1.5e-2, (s, j, pos, d)
+        sl = slice(starts[s], starts[s] + ql)
+        assert np.max(np.abs(got[sl] - other[sl])) < 2e-2, "the two kernels agree on every row"
+
+
 # ----------------------------------------------------------------------------- tcgen05 product
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (2048, 3072, 2048), (300, 520, 136), (17, 96, 80),
