@@ -75,8 +75,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [BM][ld]
   __nv_bfloat16* kv_s = q_s + BM * ld;                                    // [2 stages][K, V][BN][ld]
 
-  // the heaviest tiles (the last queries of a portion see the most keys) are launched first
-  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, head = blockIdx.y, s = blockIdx.z;
+  // the heaviest tiles (the last queries of a portion see the most keys) are launched first, for
+  // all heads before any lighter tile
+  const int tile = (int)gridDim.y - 1 - (int)blockIdx.y, head = blockIdx.x, s = blockIdx.z;
   const int q_len = seq_q_len[s];
   if (tile * BM >= q_len) return;
   const int q_start = seq_q_start[s], ctx = seq_ctx_len[s];
@@ -294,7 +295,7 @@ int launch_prefill(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((max_q_len + BM - 1) / BM, n_heads, n_seqs);
+  dim3 grid(n_heads, (max_q_len + BM - 1) / BM, n_seqs);
   attn_prefill_kernel<HD_MAX><<<grid, WARPS * 32, smem, stream>>>(q, k_pool, v_pool, out, seq_q_start, seq_q_len,
                                                                  seq_ctx_len, table_row0, pv, n_heads,
                                                                  scale * LOG2E, window);

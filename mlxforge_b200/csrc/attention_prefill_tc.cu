@@ -152,8 +152,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                  p_full = bars_u + 48, o_done = bars_u + 56;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // the heaviest tiles (the last queries of a portion see the most keys) are launched first
-  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, head = blockIdx.y, s = blockIdx.z;
+  // the heaviest tiles (the last queries of a portion see the most keys) are launched first, for
+  // all heads before any lighter tile
+  const int tile = (int)gridDim.y - 1 - (int)blockIdx.y, head = blockIdx.x, s = blockIdx.z;
   const int q_len = seq_q_len[s];
   if (tile * BM >= q_len) return;
   if (q_u & 1023u) {                                       // never seen; refused rather than computed wrongly
@@ -406,7 +407,7 @@ int launch_prefill_tc(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((max_q_len + BM - 1) / BM, n_heads, n_seqs);
+  dim3 grid(n_heads, (max_q_len + BM - 1) / BM, n_seqs);
   attn_prefill_tc_kernel<<<grid, 192, smem, stream>>>(mq, mk, mv, out, seq_q_start, seq_q_len, seq_ctx_len, table_row0,
                                                       pv, n_heads, scale * LOG2E, window, status);
   return (int)cudaGetLastError();
