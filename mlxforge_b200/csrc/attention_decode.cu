@@ -24,9 +24,6 @@ __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool v
   const int n = valid ? 16 : 0;   // src-size 0: the 16 bytes are zero-filled, nothing is read
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
 }
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
-}
 __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"

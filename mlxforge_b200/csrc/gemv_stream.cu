@@ -389,7 +389,7 @@ int launch_one(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M,
     configured = true;
   }
   const int n_tiles = (N + ROWS - 1) / ROWS;
-  // one block per SM: the block of the NEXT product fits beside it and fills its ring meanwhile
+  // two blocks per SM
   const int grid = n_tiles < 2 * n_sms ? n_tiles : 2 * n_sms;
   return (int)launch_dep(stream_kernel<NB, ROWS, OutT>, dim3(grid), dim3((CW + 1) * 32), smem, stream, x, W, out, M,
                          N, K, mode, status);
