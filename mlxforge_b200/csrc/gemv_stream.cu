@@ -371,7 +371,10 @@ int launch_tmap(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M
   const int rc = tma_host::bf16_map_chunked(W, N, K, ROWS, 128 / ROWS, &map);
   if (rc != 0) return rc;
   const int n_tiles = (N + ROWS - 1) / ROWS;
-  const int grid = n_tiles < 2 * n_sms ? n_tiles : 2 * n_sms;
+  // as many blocks as give every block the same number of tiles (to within one): 1024 tiles on
+  // 296 block slots are four rounds either way, and 256 blocks of four tiles end together
+  const int rounds = (n_tiles + 2 * n_sms - 1) / (2 * n_sms);
+  const int grid = (n_tiles + rounds - 1) / rounds;
   return (int)launch_dep(stream_tmap_kernel<NB, ROWS, T_STAGES, OutT>, dim3(grid), dim3((CW + 1) * 32), smem, stream, x, map,
                          out, M, N, K, mode, status);
 }
