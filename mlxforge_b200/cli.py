@@ -35,7 +35,8 @@ def _engine(args, **over):
     from .engine.engine import Engine, EngineConfig
     cfg = EngineConfig(model_spec=args.model, dtype=args.dtype, kv_block_size=args.kv_block_size,
                        prefill_chunk=args.prefill_chunk, skinny_mm=not args.no_skinny_mm,
-                       rope_scaling=args.rope_scaling or "", **over)
+                       rope_scaling=args.rope_scaling or "", cuda_graphs=not args.no_cuda_graphs,
+                       pipeline=not args.no_pipeline, gemm=args.gemm, **over)
     return Engine(cfg)
 
 
@@ -45,6 +46,11 @@ def _common(ap):
     ap.add_argument("--prefill-chunk", type=int, default=512)
     ap.add_argument("--no-skinny-mm", action="store_true", help="few-row products by the library instead")
     ap.add_argument("--rope-scaling", default="", help="JSON object replacing the checkpoint's rope_scaling")
+    ap.add_argument("--no-cuda-graphs", action="store_true", help="launch every kernel of a decode step one by one")
+    ap.add_argument("--no-pipeline", action="store_true",
+                    help="collect a step's tokens before the next step is launched")
+    ap.add_argument("--gemm", default="", choices=["", "auto", "library", "tcgen05"],
+                    help="many-row products: own tcgen05 kernel for gate|up (auto), the library, or the own kernel for all")
 
 
 def run_generate(args) -> int:

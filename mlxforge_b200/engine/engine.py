@@ -8,9 +8,12 @@ token ids until the request ends, ``cancel``, ``finish_reason``, ``metrics``,
 are out of scope) and in-process Python instead of a C ABI.
 
 One loop iteration = one scheduler plan, one step of the model over a mixed
-batch, one sampling call, one commit.  ``Engine.step()`` runs it on the caller's
-thread; ``Engine.start()`` runs the same loop on a worker thread, as the
-reference's single GPU thread does (src/runtime/worker.cpp:196-280).
+batch, one sampling call, one commit; the commit of a step happens in the
+iteration after the one that launched it, and while every running request is
+decoding the step after is launched first (see ``Engine.step``).
+``Engine.step()`` runs an iteration on the caller's thread; ``Engine.start()``
+runs the same loop on a worker thread, as the reference's single GPU thread
+does (src/runtime/worker.cpp:196-280).
 """
 from __future__ import annotations
 
