@@ -1,5 +1,5 @@
-// Paged causal attention of prompt portions for head size 64 on the 5th-generation tensor
-// cores: both products of a 128-query x 128-key tile are tcgen05.mma instructions with their
+// Paged causal attention of prompt portions for head sizes 64 and 128 on the 5th-generation
+// tensor cores: both products of a 128-query x 128-key tile (x 64 keys for head size 128) are tcgen05.mma instructions with their
 // results in tensor memory, the keys and values come in by TMA, and four warps do nothing
 // but the softmax.
 //
@@ -28,14 +28,24 @@
 
 namespace {
 
-constexpr int HD = 64, BM = 128, BN = 128;
-constexpr int Q_BYTES = BM * HD * 2;               // 16 KB
-constexpr int K_BYTES = BN * HD * 2;               // 16 KB
-constexpr int STAGE_BYTES = 2 * K_BYTES;           // keys then values
+// Head size 64: key tiles of 128; head size 128: key tiles of 64.  Either way a stage of keys
+// and values is 32 KB, the block's shared memory 112 KB and its tensor memory 256 columns
+// (S: BN columns, O: HD columns), so that two blocks share an SM.
+constexpr int BM = 128;
 constexpr int STAGES = 2;
-constexpr int P_BYTES = BM * BN * 2;               // 32 KB: two 128 x 64 operand tiles
-constexpr int GRAN_BYTES = 16 * HD * 2;
-constexpr int TMEM_COLS = 256;                     // S: 128 columns, O: 64
+constexpr int BOX_BYTES = 16 * 64 * 2;             // one tensor copy: 16 keys x 64 values
+constexpr int TMEM_COLS = 256;
+template <int HD, int BN> struct Shape {
+  static constexpr int SPANS = HD / 64;            // 64-wide spans of the head (a swizzled line holds one)
+  static constexpr int GRANS = BN / 16;            // granules of 16 keys per tile
+  static constexpr int Q_BYTES = BM * HD * 2;
+  static constexpr int K_BYTES = BN * HD * 2;
+  static constexpr int K_SPAN_BYTES = BN * 128;    // [BN keys][128 bytes] per span
+  static constexpr int STAGE_BYTES = 2 * K_BYTES;  // keys then values
+  static constexpr int P_BYTES = BM * BN * 2;      // BN / 64 operand tiles of 128 x 64
+  static_assert(SPANS * GRANS == 8, "eight key boxes and eight value boxes per stage");
+  static_assert(BN + HD <= TMEM_COLS, "S and O share the block's tensor memory");
+};
 constexpr unsigned WAIT_LIMIT = 1u << 26;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -137,12 +147,16 @@ __device__ __forceinline__ void sts128(unsigned addr, unsigned a, unsigned b, un
 
 int g_prefill_tc = 1;       // 0: the mma.sync kernel for every shape (mf_set_prefill_tcgen05)
 
+template <int HD, int BN>
 __global__ void __launch_bounds__(192, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
                        const int* __restrict__ seq_ctx_len, int table_row0, PagedView pv, int n_heads,
                        float scale_log2, int window, int* __restrict__ status) {
+  using SH = Shape<HD, BN>;
+  constexpr int Q_BYTES = SH::Q_BYTES, K_BYTES = SH::K_BYTES, STAGE_BYTES = SH::STAGE_BYTES, P_BYTES = SH::P_BYTES;
+  constexpr int SPANS = SH::SPANS, GRANS = SH::GRANS, K_SPAN_BYTES = SH::K_SPAN_BYTES;
   extern __shared__ __align__(1024) unsigned char smem[];      // the swizzled tiles need 1024-byte alignment
   const unsigned q_u = smem_u32(smem), kv_u = q_u + Q_BYTES, p_u = kv_u + STAGES * STAGE_BYTES;
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + Q_BYTES + STAGES * STAGE_BYTES + P_BYTES);
@@ -190,20 +204,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const unsigned tmem_base = *tmem_slot;
-  const unsigned tmem_s = tmem_base, tmem_o = tmem_base + BN;
+  const unsigned tmem_s = tmem_base, tmem_o = tmem_base + BN;     // S: columns [0, BN), O: [BN, BN + HD)
 
   if (warp == 4) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) {
-      mbar_expect_tx(q_full, Q_BYTES);      // rows past the end of q arrive as zeros
-      tma_load_2d(q_u, &map_q, head * HD, q_start + tile * BM, q_full);
-    }
+    if (lane == 0) mbar_expect_tx(q_full, Q_BYTES);      // rows past the end of q arrive as zeros
+    __syncwarp();
+    if (lane < SPANS) tma_load_2d(q_u + lane * (BM * 128), &map_q, head * HD + lane * 64, q_start + tile * BM, q_full);
     for (int i = 0; i < n_kt; i++) {
       const int kt = kt0 + i;
       const unsigned st = i % STAGES, round = i / STAGES;
-      // lanes 0..7: the key box of granule `lane`; lanes 8..15: its value box.  A granule with
-      // no visible key is not fetched.
-      const int gran = lane & 7;
+      // lanes 0..7: the key boxes (granule x span of the head); lanes 8..15: the value boxes.
+      // A granule with no visible key is not fetched.
+      const int gran = lane & (GRANS - 1), span = (lane & 7) / GRANS;
       const int key16 = kt * BN + gran * 16;
       const bool valid = lane < 16 && key16 <= pos_last && key16 + 16 > lo_first;
       int box_row = 0;
@@ -215,12 +228,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const unsigned n_valid = __popc(__ballot_sync(0xffffffffu, valid));
       if (lane == 0) {
         if (round > 0) mbar_wait(kv_empty0 + 8 * st, (round - 1) & 1, status, 41);
-        mbar_expect_tx(kv_full0 + 8 * st, n_valid * GRAN_BYTES);
+        mbar_expect_tx(kv_full0 + 8 * st, n_valid * BOX_BYTES);
       }
       __syncwarp();
       if (valid)
-        tma_load_2d(kv_u + st * STAGE_BYTES + (lane >> 3) * K_BYTES + gran * GRAN_BYTES, lane < 8 ? &map_k : &map_v,
-                    0, box_row, kv_full0 + 8 * st);
+        tma_load_2d(kv_u + st * STAGE_BYTES + (lane >> 3) * K_BYTES + span * K_SPAN_BYTES + gran * BOX_BYTES,
+                    lane < 8 ? &map_k : &map_v, span * 64, box_row, kv_full0 + 8 * st);
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------ issuer
@@ -228,7 +241,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // instruction descriptors: D float32, A and B bfloat16; N >> 3 at bit 17, M >> 4 at bit 24;
       // bit 16: B is N-major (the values)
       const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
-      const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) |
+      const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(64 >> 3) << 17) |
                                 ((unsigned)(BM >> 4) << 24);
       mbar_wait(q_full, 0, status, 42);
       for (int i = 0; i < n_kt; i++) {
@@ -236,16 +249,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         mbar_wait(kv_full0 + 8 * st, round & 1, status, 43);
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const unsigned k_addr = kv_u + st * STAGE_BYTES, v_addr = k_addr + K_BYTES;
+        // S = Q K^T: steps of 16 along the head, span after span
 #pragma unroll
-        for (int k4 = 0; k4 < HD / 16; k4++)
-          umma(tmem_s, smem_desc(q_u + k4 * 32), smem_desc(k_addr + k4 * 32), idesc_qk, k4 > 0 ? 1u : 0u);
+        for (int k = 0; k < HD / 16; k++)
+          umma(tmem_s, smem_desc(q_u + (k >> 2) * (BM * 128) + (k & 3) * 32),
+               smem_desc(k_addr + (k >> 2) * K_SPAN_BYTES + (k & 3) * 32), idesc_qk, k > 0 ? 1u : 0u);
         umma_commit(s_full);
         mbar_wait(p_full, i & 1, status, 44);           // P is in shared memory, S has been read
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        // O += P V: steps of 16 keys; a product of N = 64 for each span of the head
 #pragma unroll
-        for (int k8 = 0; k8 < BN / 16; k8++)
-          umma(tmem_o, smem_desc(p_u + (k8 >> 2) * (BM * 128) + (k8 & 3) * 32), smem_desc(v_addr + k8 * 16 * 128),
-               idesc_pv, (i > 0 || k8 > 0) ? 1u : 0u);
+        for (int k = 0; k < BN / 16; k++)
+#pragma unroll
+          for (int sp = 0; sp < SPANS; sp++)
+            umma(tmem_o + (unsigned)(sp * 64), smem_desc(p_u + (k >> 2) * (BM * 128) + (k & 3) * 32),
+                 smem_desc(v_addr + sp * K_SPAN_BYTES + k * 16 * 128), idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
         umma_commit(kv_empty0 + 8 * st);                 // the stage is free once both products have read it
         umma_commit(o_done);
       }
@@ -304,10 +322,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // ---- value rows of keys that no query of the tile may see: clear them (thread = key)
       if (key0 + BN - 1 > pos_last || key0 < lo_first) {
         const int key = key0 + r;
-        if (key > pos_last || key < lo_first) {
-          const unsigned row_u = kv_u + st * STAGE_BYTES + K_BYTES + r * 128;
+        if (r < BN && (key > pos_last || key < lo_first)) {
 #pragma unroll
-          for (int c = 0; c < 8; c++) sts128(row_u + c * 16, 0u, 0u, 0u, 0u);
+          for (int sp = 0; sp < SPANS; sp++) {
+            const unsigned row_u = kv_u + st * STAGE_BYTES + K_BYTES + sp * K_SPAN_BYTES + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; c++) sts128(row_u + c * 16, 0u, 0u, 0u, 0u);
+          }
         }
       }
       // ---- second pass: probabilities, their sum, and the row of P in the operand layout
@@ -375,10 +396,38 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
 }
 
+template <int HD, int BN>
+int launch_tc(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, __nv_bfloat16* out,
+              const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len, int table_row0, int n_seqs,
+              int max_q_len, int n_tokens, int n_heads, PagedView pv, float scale, int window, int* status,
+              cudaStream_t stream) {
+  using SH = Shape<HD, BN>;
+  CUtensorMap mq, mk, mv;
+  int rc = tma_host::bf16_map(q, n_tokens, (long long)n_heads * HD, BM, 64, &mq);
+  if (rc) return rc;
+  // the maps' row count only bounds the unit's own range check; rows beyond the pool are never asked for
+  rc = tma_host::bf16_map(k_pool, 1ll << 28, HD, 16, 64, &mk);
+  if (rc) return rc;
+  rc = tma_host::bf16_map(v_pool, 1ll << 28, HD, 16, 64, &mv);
+  if (rc) return rc;
+  const size_t smem = SH::Q_BYTES + STAGES * SH::STAGE_BYTES + SH::P_BYTES + 16 * 8 + 16;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(n_heads, (max_q_len + BM - 1) / BM, n_seqs);
+  attn_prefill_tc_kernel<HD, BN><<<grid, 192, smem, stream>>>(mq, mk, mv, out, seq_q_start, seq_q_len, seq_ctx_len,
+                                                              table_row0, pv, n_heads, scale * LOG2E, window, status);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace
 
-// 1 (the default): portions of at least 128 tokens with head size 64 take the tcgen05 kernel;
-// 0: every shape takes the mma.sync kernel.  For tests and measurements.
+// 1 (the default): portions of at least 128 tokens with head size 64 or 128 take the tcgen05
+// kernel; 0: every shape takes the mma.sync kernel.  For tests and measurements.
 MF_API int mf_set_prefill_tcgen05(int on) {
   g_prefill_tc = on ? 1 : 0;
   return 0;
@@ -390,25 +439,13 @@ int launch_prefill_tc(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
                       __nv_bfloat16* out, const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len,
                       int table_row0, int n_seqs, int max_q_len, int n_tokens, int n_heads, PagedView pv,
                       float scale, int window, int* status, cudaStream_t stream) {
-  if (!g_prefill_tc || pv.head_dim != HD || pv.page_size % 16 || max_q_len < BM || n_tokens <= 0) return MF_ERR_BAD_ARG;
+  if (!g_prefill_tc || pv.page_size % 16 || max_q_len < BM || n_tokens <= 0) return MF_ERR_BAD_ARG;
   if ((((uintptr_t)q | (uintptr_t)out) & 15) != 0) return MF_ERR_BAD_ARG;
-  CUtensorMap mq, mk, mv;
-  int rc = tma_host::bf16_map(q, n_tokens, (long long)n_heads * HD, BM, HD, &mq);
-  if (rc) return rc;
-  // the maps' row count only bounds the unit's own range check; rows beyond the pool are never asked for
-  rc = tma_host::bf16_map(k_pool, 1ll << 28, HD, 16, HD, &mk);
-  if (rc) return rc;
-  rc = tma_host::bf16_map(v_pool, 1ll << 28, HD, 16, HD, &mv);
-  if (rc) return rc;
-  const size_t smem = Q_BYTES + STAGES * STAGE_BYTES + P_BYTES + 16 * 8 + 16;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
-  dim3 grid(n_heads, (max_q_len + BM - 1) / BM, n_seqs);
-  attn_prefill_tc_kernel<<<grid, 192, smem, stream>>>(mq, mk, mv, out, seq_q_start, seq_q_len, seq_ctx_len, table_row0,
-                                                      pv, n_heads, scale * LOG2E, window, status);
-  return (int)cudaGetLastError();
+  if (pv.head_dim == 64)
+    return launch_tc<64, 128>(q, k_pool, v_pool, out, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs,
+                              max_q_len, n_tokens, n_heads, pv, scale, window, status, stream);
+  if (pv.head_dim == 128)
+    return launch_tc<128, 64>(q, k_pool, v_pool, out, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs,
+                              max_q_len, n_tokens, n_heads, pv, scale, window, status, stream);
+  return MF_ERR_BAD_ARG;
 }
