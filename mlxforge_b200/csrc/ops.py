@@ -272,8 +272,9 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], u: Optiona
     if not logits.is_cuda or logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 CUDA rows")
     n, V = logits.shape
+    split = temperature is None and V >= 16384 and n <= 4096       # greedy over a large vocabulary: two kernels
     check(library().mf_sample(logits.data_ptr(), n, V, logits.stride(0), _ptr(temperature), _ptr(u),
-                              out.data_ptr(), _stream()), "sample")
+                              out.data_ptr(), _stream()), "sample", launches=2 if split else 1)
 
 
 def apply_penalties(logits: torch.Tensor, params, histories) -> None:

@@ -99,10 +99,67 @@ sample_kernel(const float* __restrict__ logits, int V, long long row_stride,
   }
 }
 
+// Greedy rows of a large vocabulary: one block per row would read half a megabyte through one
+// SM, so ARGMAX_PARTS blocks take a part of the row each and one more kernel picks among their
+// results (lowest index among equals, as above).  The partial results live in an array of the
+// library: launches of different streams must not overlap (the engine has one stream).
+#define ARGMAX_PARTS 16
+#define ARGMAX_MAX_ROWS 4096
+__device__ float g_part_val[ARGMAX_MAX_ROWS * ARGMAX_PARTS];
+__device__ int g_part_idx[ARGMAX_MAX_ROWS * ARGMAX_PARTS];
+
+__global__ void __launch_bounds__(256)
+argmax_part_kernel(const float* __restrict__ logits, int V, long long row_stride) {
+  __shared__ float sval[8];
+  __shared__ int sidx[8];
+  const int r = blockIdx.y, part = blockIdx.x, tid = threadIdx.x;
+  const float* x = logits + (long long)r * row_stride;
+  const int per = (V + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
+  const int begin = min(V, part * per), end = min(V, begin + per);
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int i = begin + tid; i < end; i += 256) {          // ascending per thread: the first of equals stays
+    const float v = x[i];
+    if (v > best) { best = v; best_i = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float v = __shfl_xor_sync(0xffffffffu, best, o);
+    const int i = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+  }
+  if ((tid & 31) == 0) { sval[tid >> 5] = best; sidx[tid >> 5] = best_i; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < 8; w++)
+      if (sval[w] > best || (sval[w] == best && sidx[w] < best_i)) { best = sval[w]; best_i = sidx[w]; }
+    g_part_val[r * ARGMAX_PARTS + part] = best;
+    g_part_idx[r * ARGMAX_PARTS + part] = best_i;
+  }
+}
+
+__global__ void argmax_pick_kernel(int n, int* __restrict__ out) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n) return;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int p = 0; p < ARGMAX_PARTS; p++) {
+    const float v = g_part_val[r * ARGMAX_PARTS + p];
+    const int i = g_part_idx[r * ARGMAX_PARTS + p];
+    if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+  }
+  out[r] = best_i == 0x7fffffff ? 0 : best_i;          // a row of -inf: token 0, as the one-block kernel gives
+}
+
 MF_API int mf_sample(const float* logits, int n, int V, long long row_stride, const float* temperature,
                      const float* u, int* out, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (V <= 0) return MF_ERR_BAD_ARG;
+  if (temperature == nullptr && V >= 16384 && n <= ARGMAX_MAX_ROWS) {
+    argmax_part_kernel<<<dim3(ARGMAX_PARTS, n), 256, 0, stream>>>(logits, V, row_stride);
+    argmax_pick_kernel<<<(n + 127) / 128, 128, 0, stream>>>(n, out);
+    return (int)cudaGetLastError();
+  }
   sample_kernel<<<n, SAMPLE_THREADS, 0, stream>>>(logits, V, row_stride, temperature, u, out);
   return (int)cudaGetLastError();
 }
