@@ -113,3 +113,27 @@ def test_replay_with_the_tcgen05_products(models, tmp_path, mode, monkeypatch):
         got = TT.read_outputs(trace, out_dir, cfg["vocab_size"])
         d_max, where = TT.worst(got, expected)
         assert d_max <= tols["bfloat16"], (which, mode, d_max, where)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_from_the_first_token(tmp_path, dtype):
+    """Three requests decoded token by token from position 0, together: the first tokens of a
+    sequence (a context of one key), 300 steps of decoding across page edges and across the
+    widths for which decode steps are captured, a batch that shrinks as requests end."""
+    d, cfg, w = make_tiny(tmp_path, "B", "bfloat16", qk_gain=6.0)
+    reqs = {f"l{i}": random_prompt(cfg, n, 40 + i) for i, n in enumerate([300, 150, 40])}
+    expected = {rid: P.forward_logits(cfg, w, toks) for rid, toks in reqs.items()}
+    P.ROUND = P.round_bf16
+    try:
+        noise = max(float(np.max(np.abs(P.forward_logits(cfg, w, toks) - expected[rid]))) for rid, toks in reqs.items())
+    finally:
+        P.ROUND = None
+    scale = max(float(np.max(np.abs(e))) for e in expected.values())
+    tol = TOL_F32 * max(1.0, scale) if dtype == "float32" else BF16_NOISE_FACTOR * noise
+    trace = TT.lockstep(reqs)
+    out_dir = _replay(d, dtype, trace, tmp_path)
+    got = TT.read_outputs(trace, out_dir, cfg["vocab_size"])
+    assert len(got) == sum(len(t) for t in reqs.values())
+    d_max, where = TT.worst(got, expected)
+    assert d_max <= tol, (f"{dtype}: max abs diff {d_max:.3e} at {where}, first beyond tolerance {tol:.3e} at "
+                          f"{TT.first_bad(got, expected, tol)}")

@@ -61,6 +61,17 @@ def decode_tail(requests, tail=32):
     return t
 
 
+def lockstep(requests):
+    """Every request from its first token on, one token a step, all live requests in every
+    step: the first tokens of a sequence, long decoding, a batch that shrinks as requests end."""
+    t = Trace()
+    longest = max(len(toks) for toks in requests.values())
+    for p in range(longest):
+        entries = [(rid, p, toks[p:p + 1], [0]) for rid, toks in requests.items() if p < len(toks)]
+        t.add(entries, end=[rid for rid, toks in requests.items() if p == len(toks) - 1])
+    return t
+
+
 def portions(requests, sizes=(7, 2, 5, 3, 2, 11, 4, 2, 16, 1, 9)):
     """Every request alone, in portions of changing size, down to two tokens."""
     t = Trace()
