@@ -179,21 +179,24 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       }
       // ---- mask only where the tile touches the diagonal or an end of a window; online softmax
       const bool edge = kt * BN + BN - 1 > w_pos_first || kt * BN < w_lo_last;
+      if (edge) {            // a loop of its own under one branch: tiles off the diagonal pay nothing for the mask
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+          for (int j = 0; j < BN / 8; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              const int key = kt * BN + j * 8 + tq * 2 + (e & 1);
+              if (key > my_pos[mt][e >> 1] || key < my_lo[mt][e >> 1]) sc[mt][j][e] = -INFINITY;
+            }
+      }
 #pragma unroll
       for (int mt = 0; mt < MT; mt++) {
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int j = 0; j < BN / 8; j++) {
 #pragma unroll
-          for (int e = 0; e < 4; e++) {
-            float v = sc[mt][j][e];
-            if (edge) {
-              const int key = kt * BN + j * 8 + tq * 2 + (e & 1);
-              if (key > my_pos[mt][e >> 1] || key < my_lo[mt][e >> 1]) v = -INFINITY;
-              sc[mt][j][e] = v;
-            }
-            mx[e >> 1] = fmaxf(mx[e >> 1], v);
-          }
+          for (int e = 0; e < 4; e++) mx[e >> 1] = fmaxf(mx[e >> 1], sc[mt][j][e]);
         }
         float alpha[2], m_off[2];
 #pragma unroll

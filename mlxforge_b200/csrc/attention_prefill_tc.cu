@@ -145,6 +145,61 @@ __device__ __forceinline__ void sts128(unsigned addr, unsigned a, unsigned b, un
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// The two passes over a thread's row of S, in a form with the mask and one without: the mask
+// costs four integer instructions per score and pass, and all but the tiles on the diagonal
+// (or at a window's end) need none.
+template <bool EDGE, int BN>
+__device__ __forceinline__ float row_max(unsigned taddr, int key0, int my_pos, int my_lo) {
+  float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains instead of one
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; c++) {
+    float v[32];
+    tmem_ld32(taddr + (unsigned)(c * 32), v);
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+      float x = v[j];
+      if (EDGE) {
+        const int key = key0 + c * 32 + j;
+        if (key > my_pos || key < my_lo) x = -INFINITY;
+      }
+      mx4[j & 3] = fmaxf(mx4[j & 3], x);
+    }
+  }
+  return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+}
+
+template <bool EDGE, int BN>
+__device__ __forceinline__ float row_probabilities(unsigned taddr, unsigned p_row, int r, int key0, int my_pos,
+                                                   int my_lo, float scale_log2, float m_off) {
+  float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; c++) {
+    float v[32];
+    tmem_ld32(taddr + (unsigned)(c * 32), v);
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+      float x = v[j];
+      if (EDGE) {
+        const int key = key0 + c * 32 + j;
+        if (key > my_pos || key < my_lo) x = -INFINITY;
+      }
+      const float p = ex2(fmaf(x, scale_log2, -m_off));
+      v[j] = p;
+      sum4[j & 3] += p;
+    }
+    // 32 keys = four 16-byte pieces of the row's 128-byte line in half (c >> 1) of P
+    const unsigned half_u = p_row + (c >> 1) * (BM * 128);
+#pragma unroll
+    for (int q4 = 0; q4 < 4; q4++) {
+      const int piece = (c & 1) * 4 + q4;
+      sts128(half_u + ((piece ^ (r & 7)) << 4), pack_bf16(v[q4 * 8 + 0], v[q4 * 8 + 1]),
+             pack_bf16(v[q4 * 8 + 2], v[q4 * 8 + 3]), pack_bf16(v[q4 * 8 + 4], v[q4 * 8 + 5]),
+             pack_bf16(v[q4 * 8 + 6], v[q4 * 8 + 7]));
+    }
+  }
+  return (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+}
+
 int g_prefill_tc = 1;       // 0: the mma.sync kernel for every shape (mf_set_prefill_tcgen05)
 
 template <int HD, int BN>
@@ -285,21 +340,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // mask only where the tile touches this warp's diagonal or an end of its windows
       const bool edge = key0 + BN - 1 > w_pos_first || key0 < w_lo_last;
       // ---- first pass over the row of S: its maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        float v[32];
-        tmem_ld32(tmem_s + lane_field + (unsigned)(c * 32), v);
-#pragma unroll
-        for (int j = 0; j < 32; j++) {
-          float x = v[j];
-          if (edge) {
-            const int key = key0 + c * 32 + j;
-            if (key > my_pos || key < my_lo) x = -INFINITY;
-          }
-          mx = fmaxf(mx, x);
-        }
-      }
+      float mx = edge ? row_max<true, BN>(tmem_s + lane_field, key0, my_pos, my_lo)
+                      : row_max<false, BN>(tmem_s + lane_field, key0, my_pos, my_lo);
       mx *= scale_log2;                                      // scale > 0: the max commutes with it
       const float m_new = fmaxf(m_row, mx);
       const float m_off = (m_new == -INFINITY) ? 0.f : m_new;
@@ -332,33 +374,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
       // ---- second pass: probabilities, their sum, and the row of P in the operand layout
-      float sum = 0.f;
       const unsigned p_row = p_u + (r >> 3) * 1024 + (r & 7) * 128;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        float v[32];
-        tmem_ld32(tmem_s + lane_field + (unsigned)(c * 32), v);
-#pragma unroll
-        for (int j = 0; j < 32; j++) {
-          float x = v[j];
-          if (edge) {
-            const int key = key0 + c * 32 + j;
-            if (key > my_pos || key < my_lo) x = -INFINITY;
-          }
-          const float p = ex2(fmaf(x, scale_log2, -m_off));
-          v[j] = p;
-          sum += p;
-        }
-        // 32 keys = four 16-byte pieces of the row's 128-byte line in half (c >> 1) of P
-        const unsigned half_u = p_row + (c >> 1) * (BM * 128);
-#pragma unroll
-        for (int q4 = 0; q4 < 4; q4++) {
-          const int piece = (c & 1) * 4 + q4;
-          sts128(half_u + ((piece ^ (r & 7)) << 4), pack_bf16(v[q4 * 8 + 0], v[q4 * 8 + 1]),
-                 pack_bf16(v[q4 * 8 + 2], v[q4 * 8 + 3]), pack_bf16(v[q4 * 8 + 4], v[q4 * 8 + 5]),
-                 pack_bf16(v[q4 * 8 + 6], v[q4 * 8 + 7]));
-        }
-      }
+      const float sum = edge ? row_probabilities<true, BN>(tmem_s + lane_field, p_row, r, key0, my_pos, my_lo, scale_log2, m_off)
+                             : row_probabilities<false, BN>(tmem_s + lane_field, p_row, r, key0, my_pos, my_lo, scale_log2, m_off);
       l_row = l_row * alpha + sum;
       m_row = m_new;
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");     // P and the cleared rows, before the product reads them
