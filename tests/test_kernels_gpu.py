@@ -170,6 +170,9 @@ ATTN_CASES = [
     (3, 1, 256, [70], 0),
     (40, 2, 64, [90, 33], 0),          # 20 query heads per KV head: two groups of 16
     (4, 2, 32, [300, 40, 129], 37),    # a window
+    (8, 2, 64, [3000, 700, 45], 0),    # head size 64 over several splits of the keys
+    (8, 2, 64, [1500, 300], 600),      # a window that spans splits and tiles
+    (4, 4, 64, [2100, 129], 100),      # a window inside one tile, far from the start
 ]
 
 
