@@ -42,14 +42,17 @@ class AttentionMixer(Mixer):
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         q, kv = self.n_heads * self.hd, self.n_kv * self.hd
-        return {
+        specs = {
             self.prefix + "q_proj.weight": TensorSpec((q, self.hidden)),
             self.prefix + "k_proj.weight": TensorSpec((kv, self.hidden)),
             self.prefix + "v_proj.weight": TensorSpec((kv, self.hidden)),
             self.prefix + "o_proj.weight": TensorSpec((self.hidden, q)),
         }
+        specs.update(self.position.tensor_specs())      # a position encoding may have tensors of its own
+        return specs
 
     def bind(self, tensors) -> None:
+        self.position.bind(tensors)
         dt = self.rt.dtype
         self.w_qkv = torch.cat([tensors[self.prefix + n + "_proj.weight"].to(dt) for n in ("q", "k", "v")],
                                dim=0).contiguous()

@@ -149,6 +149,16 @@ class Norm(Part):
 class PositionEncoding(Part):
     """Turns integer positions into whatever the mixer applies to queries and keys."""
 
+    def rotate_and_store(self, qkv, batch, q_out, lane, n_heads, n_kv_heads, writes_cache: bool) -> None:
+        """``qkv``: [T, (n_heads + 2 n_kv_heads) * head_dim], the step's projections side by
+        side.  Writes the encoded queries to ``q_out`` [T, n_heads * head_dim] and, if
+        ``writes_cache``, the encoded keys and the values of token ``t`` into page
+        ``batch.block_table(lane.group)[batch.seq_of_token[t], p // lane.page_size]``, slot
+        ``p % lane.page_size`` of ``lane.k`` / ``lane.v`` ([page, kv_head, slot, head_dim]),
+        with ``p = batch.positions[t]``.  The mixer forwards this part's ``tensor_specs`` and
+        ``bind``, so an encoding may own tensors."""
+        raise NotImplementedError
+
 
 class Mixer(Part):
     def cache_need(self) -> CacheNeed:

@@ -1,6 +1,7 @@
 """Generality of the parts: a toy architecture defined HERE — a mixer with
-fixed-size state of its own, a feed-forward with routing, layers with different
-mixers, a windowed attention layer without position encoding, a schedule that
+fixed-size state of its own, a feed-forward with routing, a position encoding with
+tensors of its own, layers with different mixers, a windowed attention layer
+without position encoding, a schedule that
 runs one layer twice and lets one run read another run's cache — is registered,
 built from a model folder and stepped through the engine's own loader, cache
 manager and step function, with no change to the framework's files.  Its logits,
@@ -19,6 +20,7 @@ pytestmark = pytest.mark.gpu
 
 H, V, D_STATE, N_EXPERTS, INTER = 48, 97, 24, 3, 40
 NH, NKV, HD, WINDOW = 3, 1, 16, 21
+N_POS = 29
 DECAY = 0.8
 EPS = 1e-5
 
@@ -30,7 +32,8 @@ def _register():
     from mlxforge_b200.config.model_config import ModelConfig
     from mlxforge_b200.config.registry import register_architecture
     from mlxforge_b200.parts.base import (FeedForward, FixedState, LayerSpec, Mixer, ModelSpec, PartSpec,
-                                          ScheduleItem, TensorSpec, register_feed_forward, register_mixer)
+                                          PositionEncoding, ScheduleItem, TensorSpec, register_feed_forward,
+                                          register_mixer, register_position)
 
     class DecayStateMixer(Mixer):
         """s_t = decay * s_{t-1} + x_t W_in^T ;  out_t = s_t W_out^T.  The state s lives in
@@ -93,6 +96,34 @@ def _register():
                     out[rows] = y * probs[rows, k:k + 1]
             return out.to(x.dtype)
 
+    class LearnedPositions(PositionEncoding):
+        """Learned vectors added to queries and keys: q += A[pos mod n], k += B[pos mod n], the same
+        for every head.  It owns two tensors and writes keys and values into the step's pages itself."""
+
+        def __init__(self, params, prefix, runtime):
+            super().__init__(params, prefix, runtime)
+            self.hd, self.n = params["head_dim"], params["n_positions"]
+
+        def tensor_specs(self):
+            return {self.prefix + "q.weight": TensorSpec((self.n, self.hd)),
+                    self.prefix + "k.weight": TensorSpec((self.n, self.hd))}
+
+        def bind(self, tensors):
+            self.a = tensors[self.prefix + "q.weight"].float()
+            self.b = tensors[self.prefix + "k.weight"].float()
+
+        def rotate_and_store(self, qkv, batch, q_out, lane, n_heads, n_kv_heads, writes_cache):
+            T, hd = qkv.shape[0], self.hd
+            pos, seq = batch.positions.long(), batch.seq_of_token.long()
+            q, k, v = qkv.float().split([n_heads * hd, n_kv_heads * hd, n_kv_heads * hd], dim=1)
+            q_out.copy_((q.view(T, n_heads, hd) + self.a[pos % self.n][:, None]).reshape(T, -1).to(q_out.dtype))
+            if writes_cache:
+                page = batch.block_table(lane.group).long()[seq, pos // lane.page_size]
+                slot = pos % lane.page_size
+                lane.k[page, :, slot] = (k.view(T, n_kv_heads, hd) + self.b[pos % self.n][:, None]).to(lane.k.dtype)
+                lane.v[page, :, slot] = v.view(T, n_kv_heads, hd).to(lane.v.dtype)
+
+    register_position("toy_learned", LearnedPositions, replace=True)
     register_mixer("toy_decay_state", DecayStateMixer, replace=True)
     register_feed_forward("toy_top1_experts", Top1Experts, replace=True)
 
@@ -107,6 +138,7 @@ def _register():
     def build(cfg):
         rope = PartSpec("rope", {"head_dim": HD, "rotary_dim": HD, "theta": 10000.0, "scaling": None})
         nope = PartSpec("none", {"head_dim": HD})
+        learned = PartSpec("toy_learned", {"head_dim": HD, "n_positions": N_POS}, prefix="layers.4.pos.")
 
         def attn(i, position, window):
             return PartSpec("attention", {"hidden_size": H, "n_heads": NH, "n_kv_heads": NKV, "head_dim": HD,
@@ -123,10 +155,12 @@ def _register():
                       norm("layers.1.n2.")),
             LayerSpec("prenorm", attn(2, nope, WINDOW), norm("layers.2.n1."), swiglu(2), norm("layers.2.n2.")),
             LayerSpec("prenorm", attn(3, rope, 0), norm("layers.3.n1."), swiglu(3), norm("layers.3.n2.")),
+            LayerSpec("prenorm", attn(4, learned, 0), norm("layers.4.n1."), swiglu(4), norm("layers.4.n2.")),
         )
         # layer 0 runs twice (two caches of its own); the last run of layer 3 reads the cache
         # that the first run of layer 0 wrote and writes none
-        schedule = (ScheduleItem(0), ScheduleItem(1), ScheduleItem(2), ScheduleItem(0), ScheduleItem(3, cache_of=0))
+        schedule = (ScheduleItem(0), ScheduleItem(1), ScheduleItem(2), ScheduleItem(0), ScheduleItem(3, cache_of=0),
+                    ScheduleItem(4))
         return ModelSpec(hidden_size=H, vocab_size=V,
                          embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, prefix="embed."),
                          layers=layers, schedule=schedule, final_norm=norm("final_norm."),
@@ -140,10 +174,12 @@ def toy_weights(seed=3):
     rng = np.random.default_rng(seed)
     r = lambda *s, std=0.08: bf16_round(rng.standard_normal(s).astype(np.float32) * std)
     w = {"embed.weight": r(V, H, std=0.5), "final_norm.weight": bf16_round(1 + 0.1 * rng.standard_normal(H).astype(np.float32))}
-    for i in range(4):
+    for i in range(5):
         for n in ("n1", "n2"):
             w[f"layers.{i}.{n}.weight"] = bf16_round(1 + 0.1 * rng.standard_normal(H).astype(np.float32))
-    for i in (0, 2, 3):
+    w["layers.4.pos.q.weight"] = r(N_POS, HD, std=0.5)
+    w["layers.4.pos.k.weight"] = r(N_POS, HD, std=0.5)
+    for i in (0, 2, 3, 4):
         w[f"layers.{i}.attn.q_proj.weight"] = r(NH * HD, H, std=0.3)
         w[f"layers.{i}.attn.k_proj.weight"] = r(NKV * HD, H, std=0.3)
         w[f"layers.{i}.attn.v_proj.weight"] = r(NKV * HD, H)
@@ -175,7 +211,10 @@ def plain_forward(w, tokens):
         xn = P.rms_norm(h, w[p + "n1.weight"], EPS)
         q, k, v = P.project_qkv(xn, w[p + "attn.q_proj.weight"], w[p + "attn.k_proj.weight"],
                                 w[p + "attn.v_proj.weight"], NH, NKV, HD)
-        if rope:
+        if rope == "learned":
+            q = q + w["layers.4.pos.q.weight"][pos % N_POS][None]
+            k = k + w["layers.4.pos.k.weight"][pos % N_POS][None]
+        elif rope:
             q, k = P.apply_rope(q, pos, freqs), P.apply_rope(k, pos, freqs)
         if kv_from is not None:
             k, v = kept[kv_from]
@@ -208,6 +247,7 @@ def plain_forward(w, tokens):
     h = attn_block(h, 2, 2, False, WINDOW)
     h = attn_block(h, 0, 3, True, 0)
     h = attn_block(h, 3, 4, True, 0, kv_from=0)
+    h = attn_block(h, 4, 5, "learned", 0)
     return P.rms_norm(h, w["final_norm.weight"], EPS) @ w["embed.weight"].T
 
 
@@ -224,7 +264,7 @@ def test_toy_architecture_is_registered_built_and_stepped(tmp_path):
     runner = make_runner(d, "float32", max_tokens=192)
     layout = runner.model.cache_layout
     # two paged groups (full attention: three lanes; windowed: one) and one state group
-    assert sorted((g.need.window, g.n_lanes) for g in layout.paged) == [(0, 2), (WINDOW, 1)]
+    assert sorted((g.need.window, g.n_lanes) for g in layout.paged) == [(0, 3), (WINDOW, 1)]
     assert [(type(g.need), g.n_lanes) for g in layout.state] == [(FixedState, 1)]
     assert layout.item_lane[4] == layout.item_lane[0], "the last run reads the first run's lane"
 
