@@ -35,6 +35,13 @@ LLAMA_1B = {
                      "original_max_position_embeddings": 8192},
     "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": True,
 }
+# configs[3] and [4]: the other shapes that the reference's benchmark names (--shape, for measurements
+# beside the headline; the default run is the 1B shape)
+LLAMA_3B = dict(LLAMA_1B, num_hidden_layers=28, hidden_size=3072, num_attention_heads=24, head_dim=128)
+LLAMA_8B = dict(LLAMA_1B, num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, head_dim=128,
+                intermediate_size=14336, tie_word_embeddings=False,
+                rope_scaling=dict(LLAMA_1B["rope_scaling"], factor=8.0))
+SHAPES = {"1b": ("Llama-3.2-1B", LLAMA_1B), "3b": ("Llama-3.2-3B", LLAMA_3B), "8b": ("Llama-3.1-8B", LLAMA_8B)}
 CONTEXT = 8192
 BATCH = 8
 PREFILL_TOKENS = 2048
@@ -216,7 +223,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=LLAMA_1B["num_hidden_layers"])
+    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes (default: the 1B shape)")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all)")
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch")
     ap.add_argument("--batch", type=int, default=BATCH)
@@ -236,11 +244,13 @@ def main() -> int:
     import mlxforge_b200 as mf
     from mlxforge_b200.config import config_from_json
 
-    cfg_json = dict(LLAMA_1B, num_hidden_layers=args.layers)
+    shape_name, shape = SHAPES[args.shape]
+    args.layers = args.layers or shape["num_hidden_layers"]
+    cfg_json = dict(shape, num_hidden_layers=args.layers)
     tmp = tempfile.mkdtemp(prefix="mlxforge_bench_")
     try:
         t0 = time.time()
-        model_dir = mf.write_random_model(os.path.join(tmp, "llama_1b_random"), config_from_json(cfg_json), seed=0,
+        model_dir = mf.write_random_model(os.path.join(tmp, f"llama_{args.shape}_random"), config_from_json(cfg_json), seed=0,
                                           dtype="bfloat16")
         ctx = args.context
         pool_seqs = 64 if args.only == "all" and not args.skip_points else max(args.batch, 1)
@@ -259,7 +269,7 @@ def main() -> int:
 
     if args.only == "prefill":
         t_pre = prefill_device(engine, PREFILL_TOKENS, runs=max(1, args.steps), warmup=args.warmup)
-        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(t_pre * 1e3, 3),
+        print(json.dumps({"only": "prefill", "shape": args.shape, "tokens": PREFILL_TOKENS, "ms": round(t_pre * 1e3, 3),
                           "layers": args.layers}))
         return 0
     BATCH_ = args.batch
@@ -267,13 +277,14 @@ def main() -> int:
     clocks.start()
     sec, launches, kv_tokens = decode_device(engine, BATCH_, ctx, args.steps, args.warmup)
     clk = clocks.stop()
-    if args.only == "decode":
-        print(json.dumps({"only": "decode", "batch": BATCH_, "context": ctx, "layers": args.layers,
-                          "ms_per_step": round(sec * 1e3, 4), "launches_per_step": launches}))
-        return 0
     value = BATCH_ / sec
     bytes_step = weight_bytes + kv_tokens * kv_per_token
     achieved = bytes_step / sec / 1e9
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "shape": args.shape, "batch": BATCH_, "context": ctx, "layers": args.layers,
+                          "ms_per_step": round(sec * 1e3, 4), "launches_per_step": launches,
+                          "gbs": round(achieved, 1)}))
+        return 0
 
     points = {}
     if not args.skip_points:
@@ -294,12 +305,13 @@ def main() -> int:
     e2e_value, h2d, d2h = decode_e2e(engine, BATCH_, ctx, args.steps, args.warmup)
 
     line = {
-        "metric": f"decode tok/s @ batch {BATCH_} (Llama-3.2-1B bf16)", "value": round(value, 1), "unit": "tokens/s",
+        "metric": f"decode tok/s @ batch {BATCH_} ({shape_name} bf16)", "value": round(value, 1), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded normal(0, 0.02) weights, seeded uniform token ids, random cache contents",
         "config": {
-            "model": "Llama-3.2-1B shape (LlamaForCausalLM)", "layers": L, "layers_of_named_config": 16,
+            "model": f"{shape_name} shape (LlamaForCausalLM)", "layers": L,
+            "layers_of_named_config": shape["num_hidden_layers"],
             "hidden": H, "heads": nh, "kv_heads": nkv, "head_dim": hd, "intermediate": I, "vocab": V,
             "global_batch": BATCH_, "seq_len": ctx, "context_len": ctx, "kv_block": engine.cache.page_size,
             "prefill_tokens": T, "parallelism": "single GPU",
