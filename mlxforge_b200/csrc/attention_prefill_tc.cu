@@ -1,25 +1,28 @@
 // Paged causal attention of prompt portions for head sizes 64 and 128 on the 5th-generation
-// tensor cores: both products of a 128-query x 128-key tile (x 64 keys for head size 128) are tcgen05.mma instructions with their
-// results in tensor memory, the keys and values come in by TMA, and four warps do nothing
-// but the softmax.
+// tensor cores: both products of a tile of 128 queries x 64 keys are tcgen05.mma instructions
+// with their results in tensor memory, the keys and values come in by TMA, and four warps do
+// nothing but the softmax.
 //
-// A block takes 128 consecutive queries of one head of one sequence and walks the key tiles
-// its queries can see, lowest first:
-//   warp 4   (producer) one tensor copy per granule of 16 keys (a page holds whole granules):
-//            8 key boxes and 8 value boxes per tile, 128-byte swizzled, into a ring of two
-//            stages; the queries' own tile once at the start;
-//   warp 5   (issuer) one thread: S = Q K^T (M 128, N 128, four steps of K 16 over the head)
-//            into tensor memory, then, when the softmax warps have left P in shared memory,
-//            O += P V (M 128, N 64, eight steps of 16 keys; V is the N-major operand: its rows
-//            are keys, its 128-byte lines run along the head);
-//   warps 0-3 a query row per thread (a lane of tensor memory): read the row of S, mask where
-//            the tile touches the diagonal or a window's end, running maximum and sum in
-//            float32, rescale the row of O in tensor memory when the maximum moved, write the
-//            row of P as bfloat16 in the operand layout, at the end divide and store.
-// Two blocks share an SM (112 KB of shared memory and 256 columns of tensor memory each), so
-// one block's softmax runs under the other's products.  Keys outside every query's range in
-// a tile may be stale memory: their scores are masked by selection, and their value rows are
-// cleared in shared memory before the second product (0 x NaN would poison it).
+// A block takes 128 consecutive queries of one head of one sequence and walks the tiles of 64
+// keys its queries can see, lowest first:
+//   warp 4   (producer) one tensor copy per granule of 16 keys (a page holds whole granules)
+//            and 64-wide span of the head, 128-byte swizzled, into a ring of stages; the
+//            queries' own tile once at the start;
+//   warp 5   (issuer) one thread: S = Q K^T (M 128, N 64, steps of K 16 over the head) into
+//            tensor memory, then, when the softmax warps have left P in shared memory,
+//            O += P V (M 128, N 64 per span of the head, four steps of 16 keys; V is the
+//            N-major operand: its rows are keys, its 128-byte lines run along the head);
+//   warps 0-3 a query row per thread (a lane of tensor memory): read the row of S once into
+//            registers, mask it where the tile touches the diagonal or a window's end, running
+//            maximum and sum in float32, rescale the row of O in tensor memory when the
+//            exponent's reference moves (rarely: see MAX_SLACK_LOG2), write the row of P as
+//            bfloat16 in the operand layout, at the end divide and store.
+// Two blocks share an SM (112 KB of shared memory and 256 columns of tensor memory each).
+// Head size 128 has one S per block, so one block's softmax runs under the other block's
+// products; head size 64 has room for two S per block and issues its products two tiles
+// ahead of the softmax (the second kernel below).  Keys outside every query's range in a tile
+// may be stale memory: their scores are masked by selection, and their value rows are cleared
+// in shared memory before the second product (0 x NaN would poison it).
 //
 // Every wait is bounded (codes 41-47 in `status`), and the tensor memory is freed in every
 // case.  Formula: src/model/sdpa.cpp:71-95; the reference calls its library's fused kernel.
@@ -28,9 +31,9 @@
 
 namespace {
 
-// Head size 64: key tiles of 128; head size 128: key tiles of 64.  Either way a stage of keys
-// and values is 32 KB, the block's shared memory 112 KB and its tensor memory 256 columns
-// (S: BN columns, O: HD columns), so that two blocks share an SM.
+// The kernel with one S (head size 128): key tiles of 64, a stage of keys and values is 32 KB,
+// the block's shared memory 112 KB and its tensor memory 256 columns (S: BN columns, O: HD
+// columns), so that two blocks share an SM.
 constexpr int BM = 128;
 constexpr int STAGES = 2;
 constexpr int BOX_BYTES = 16 * 64 * 2;             // one tensor copy: 16 keys x 64 values
@@ -44,10 +47,17 @@ template <int HD, int BN> struct Shape {
   static constexpr int STAGE_BYTES = 2 * K_BYTES;  // keys then values
   static constexpr int P_BYTES = BM * BN * 2;      // BN / 64 operand tiles of 128 x 64
   static_assert(SPANS * GRANS == 8, "eight key boxes and eight value boxes per stage");
+  static_assert(BN == 64, "a row of S is read into registers as two loads of 32 columns");
   static_assert(BN + HD <= TMEM_COLS, "S and O share the block's tensor memory");
 };
 constexpr unsigned WAIT_LIMIT = 1u << 26;
 constexpr float LOG2E = 1.4426950408889634f;
+// The exponent's reference for a row is its running maximum, but it need not be THE maximum:
+// any reference cancels in O / l.  A warp moves its rows' references (and rescales its rows of
+// O in tensor memory, a load, 64 multiplications and a store per row) only when some row's
+// maximum has grown by more than 2^8 since the last move; until then probabilities may reach
+// 256, which float32 sums and bfloat16's eight exponent bits hold as well as values below one.
+constexpr float MAX_SLACK_LOG2 = 8.0f;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
@@ -168,65 +178,56 @@ __device__ __forceinline__ void sts128(unsigned addr, unsigned a, unsigned b, un
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-// The two passes over a thread's row of S, in a form with the mask and one without: the mask
-// costs four integer instructions per score and pass, and all but the tiles on the diagonal
-// (or at a window's end) need none.  With AHEAD the row's next 32 columns are on their way
-// from tensor memory while the current 32 are worked on (the loop is then unrolled, with two
-// sets of registers); without it each load is waited for before anything else.
-template <bool EDGE, int BN, bool AHEAD>
-__device__ __forceinline__ float row_max(unsigned taddr, int key0, int my_pos, int my_lo) {
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// A thread's row of S for 64 keys: read from tensor memory ONCE into `u` (both loads on their
+// way before the first is waited for), masked in place where the tile touches the diagonal or a
+// window's end (all other tiles take the form without the mask: four integer instructions per
+// score less), and its maximum returned.  The second pass works on the registers.
+template <bool EDGE>
+__device__ __forceinline__ float row_scores_max(unsigned taddr, unsigned (&u)[2][32], int key0, int my_pos, int my_lo) {
+  tmem_ld32_issue(taddr, u[0]);
+  tmem_ld32_issue(taddr + 32u, u[1]);
   float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains instead of one
-  unsigned u[AHEAD ? 2 : 1][32];
-  if (AHEAD) tmem_ld32_issue(taddr, u[0]);
-#pragma unroll(AHEAD ? BN / 32 : 1)
-  for (int c = 0; c < BN / 32; c++) {
-    unsigned (&cur)[32] = u[AHEAD ? (c & 1) : 0];
-    if (!AHEAD) tmem_ld32_issue(taddr + (unsigned)(c * 32), cur);
-    tmem_ld32_landed(cur);
-    if (AHEAD && c + 1 < BN / 32) tmem_ld32_issue(taddr + (unsigned)((c + 1) * 32), u[AHEAD ? ((c + 1) & 1) : 0]);
 #pragma unroll
-    for (int j = 0; j < 32; j++) {
-      float x = __uint_as_float(cur[j]);
-      if (EDGE) {
+  for (int c = 0; c < 2; c++) {
+    tmem_ld32_landed(u[c]);                      // waits for both; the second call finds them there
+    if (EDGE) {
+#pragma unroll
+      for (int j = 0; j < 32; j++) {
         const int key = key0 + c * 32 + j;
-        if (key > my_pos || key < my_lo) x = -INFINITY;
+        if (key > my_pos || key < my_lo) u[c][j] = __float_as_uint(-INFINITY);
       }
-      mx4[j & 3] = fmaxf(mx4[j & 3], x);
     }
+#pragma unroll
+    for (int j = 0; j < 32; j += 2)
+      mx4[(j >> 1) & 3] = fmax3(mx4[(j >> 1) & 3], __uint_as_float(u[c][j]), __uint_as_float(u[c][j + 1]));
   }
   return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
 }
 
-template <bool EDGE, int BN, bool AHEAD>
-__device__ __forceinline__ float row_probabilities(unsigned taddr, unsigned p_row, int r, int key0, int my_pos,
-                                                   int my_lo, float scale_log2, float m_off) {
+// Second pass: probabilities (in place), their sum, and the row of P as bfloat16 in the operand
+// layout: 64 keys = the eight 16-byte pieces of the row's 128-byte line.
+__device__ __forceinline__ float row_probabilities(unsigned (&u)[2][32], unsigned p_row, int r, float scale_log2,
+                                                   float m_off) {
   float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-  unsigned u[AHEAD ? 2 : 1][32];
-  if (AHEAD) tmem_ld32_issue(taddr, u[0]);
-#pragma unroll(AHEAD ? BN / 32 : 1)
-  for (int c = 0; c < BN / 32; c++) {
-    unsigned (&cur)[32] = u[AHEAD ? (c & 1) : 0];
-    if (!AHEAD) tmem_ld32_issue(taddr + (unsigned)(c * 32), cur);
-    tmem_ld32_landed(cur);
-    if (AHEAD && c + 1 < BN / 32) tmem_ld32_issue(taddr + (unsigned)((c + 1) * 32), u[AHEAD ? ((c + 1) & 1) : 0]);
-    float v[32];
+#pragma unroll
+  for (int c = 0; c < 2; c++) {
+    float (&v)[32] = reinterpret_cast<float (&)[32]>(u[c]);
 #pragma unroll
     for (int j = 0; j < 32; j++) {
-      float x = __uint_as_float(cur[j]);
-      if (EDGE) {
-        const int key = key0 + c * 32 + j;
-        if (key > my_pos || key < my_lo) x = -INFINITY;
-      }
-      const float p = ex2(fmaf(x, scale_log2, -m_off));
+      const float p = ex2(fmaf(v[j], scale_log2, -m_off));
       v[j] = p;
       sum4[j & 3] += p;
     }
-    // 32 keys = four 16-byte pieces of the row's 128-byte line in half (c >> 1) of P
-    const unsigned half_u = p_row + (c >> 1) * (BM * 128);
 #pragma unroll
     for (int q4 = 0; q4 < 4; q4++) {
-      const int piece = (c & 1) * 4 + q4;
-      sts128(half_u + ((piece ^ (r & 7)) << 4), pack_bf16(v[q4 * 8 + 0], v[q4 * 8 + 1]),
+      const int piece = c * 4 + q4;
+      sts128(p_row + ((piece ^ (r & 7)) << 4), pack_bf16(v[q4 * 8 + 0], v[q4 * 8 + 1]),
              pack_bf16(v[q4 * 8 + 2], v[q4 * 8 + 3]), pack_bf16(v[q4 * 8 + 4], v[q4 * 8 + 5]),
              pack_bf16(v[q4 * 8 + 6], v[q4 * 8 + 7]));
     }
@@ -236,7 +237,7 @@ __device__ __forceinline__ float row_probabilities(unsigned taddr, unsigned p_ro
 
 int g_prefill_tc = 1;       // 0: the mma.sync kernel for every shape (mf_set_prefill_tcgen05)
 
-template <int HD, int BN, bool AHEAD>
+template <int HD, int BN>
 __global__ void __launch_bounds__(192, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
@@ -374,17 +375,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // mask only where the tile touches this warp's diagonal or an end of its windows
       const bool edge = key0 + BN - 1 > w_pos_first || key0 < w_lo_last;
       // ---- first pass over the row of S: its maximum
-      float mx = edge ? row_max<true, BN, AHEAD>(tmem_s + lane_field, key0, my_pos, my_lo)
-                      : row_max<false, BN, AHEAD>(tmem_s + lane_field, key0, my_pos, my_lo);
+      unsigned sc[2][32];
+      float mx = edge ? row_scores_max<true>(tmem_s + lane_field, sc, key0, my_pos, my_lo)
+                      : row_scores_max<false>(tmem_s + lane_field, sc, key0, my_pos, my_lo);
       mx *= scale_log2;                                      // scale > 0: the max commutes with it
-      const float m_new = fmaxf(m_row, mx);
+      const float m_cand = fmaxf(m_row, mx);
+      const bool moved = __any_sync(0xffffffffu, m_cand - m_row > MAX_SLACK_LOG2);      // also from -inf
+      const float m_new = moved ? m_cand : m_row;
       const float m_off = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = (m_row == -INFINITY) ? 0.f : ex2(m_row - m_off);
+      const float alpha = !moved ? 1.f : ((m_row == -INFINITY) ? 0.f : ex2(m_row - m_off));
       // ---- the product before this one has read P and left O: rescale O if a maximum moved
       if (i > 0) {
         mbar_wait(o_done, (i - 1) & 1, status, 46);
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        if (__any_sync(0xffffffffu, m_new != m_row)) {
+        if (moved) {
 #pragma unroll 1
           for (int c = 0; c < HD / 32; c++) {
             float v[32];
@@ -409,9 +413,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       // ---- second pass: probabilities, their sum, and the row of P in the operand layout
       const unsigned p_row = p_u + (r >> 3) * 1024 + (r & 7) * 128;
-      const float sum =
-          edge ? row_probabilities<true, BN, AHEAD>(tmem_s + lane_field, p_row, r, key0, my_pos, my_lo, scale_log2, m_off)
-               : row_probabilities<false, BN, AHEAD>(tmem_s + lane_field, p_row, r, key0, my_pos, my_lo, scale_log2, m_off);
+      const float sum = row_probabilities(sc, p_row, r, scale_log2, m_off);
       l_row = l_row * alpha + sum;
       m_row = m_new;
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");     // P and the cleared rows, before the product reads them
@@ -449,6 +451,246 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Head size 64 with the products running AHEAD of the softmax.  The kernel above has one S in
+// tensor memory, so within a block S = Q K^T, the softmax and O += P V take turns and only the
+// SM's other block fills the gaps.  Here a block works on sub-tiles of 64 keys and has two
+// S buffers (tensor memory: S0 64 columns, S1 64, O 64): while the softmax warps work on
+// sub-tile j, S of sub-tile j + 1 is already there and that of j + 2 is issued as soon as P of
+// j has been handed over, right behind O += P_j V_j.  The softmax warps never wait for a
+// product in the steady state.  Keys and values come in stages of 64 keys (8 KB each, four
+// tensor copies of 16 keys) through a ring of five, so that the keys two sub-tiles ahead are
+// there when their product is issued.  P stays single: a softmax pass writes it only after
+// it has waited for the previous O += P V (which it needs anyway before it rescales O).
+namespace ahead {
+constexpr int HD = 64, SUB = 64, RING = 5;
+constexpr int Q_BYTES = BM * HD * 2, K_BYTES = SUB * HD * 2, STAGE_BYTES = 2 * K_BYTES, P_BYTES = BM * SUB * 2;
+constexpr size_t SMEM = Q_BYTES + RING * STAGE_BYTES + P_BYTES + 16 * 8 + 16;
+}  // namespace ahead
+
+__global__ void __launch_bounds__(192, 2)
+attn_prefill_tc_ahead_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                             const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
+                             const int* __restrict__ seq_ctx_len, int table_row0, PagedView pv, int n_heads,
+                             float scale_log2, int window, int* __restrict__ status) {
+  using namespace ahead;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const unsigned q_u = smem_u32(smem), kv_u = q_u + Q_BYTES, p_u = kv_u + RING * STAGE_BYTES;
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + Q_BYTES + RING * STAGE_BYTES + P_BYTES);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 16);
+  const unsigned bars_u = smem_u32(bars);
+  const unsigned q_full = bars_u, kv_full0 = bars_u + 8, kv_empty0 = kv_full0 + 8 * RING, s_full0 = kv_empty0 + 8 * RING,
+                 p_full = s_full0 + 16, o_done = p_full + 8;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = (int)gridDim.y - 1 - (int)blockIdx.y, head = blockIdx.x, s = blockIdx.z;
+  const int q_len = seq_q_len[s];
+  if (tile * BM >= q_len) return;
+  if (q_u & 1023u) {
+    if (threadIdx.x == 0 && status) atomicExch(status, 40);
+    return;
+  }
+  const int q_start = seq_q_start[s], ctx = seq_ctx_len[s];
+  const int seq_row = table_row0 + s;
+  const int p0 = ctx - q_len;
+  const int kvh = head / (n_heads / pv.n_kv_heads);
+  const int rows = min(BM, q_len - tile * BM);
+  const int pos_first = p0 + tile * BM, pos_last = pos_first + rows - 1;
+  const int lo_first = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+  const int sub0 = lo_first / SUB, n_sub = pos_last / SUB - sub0 + 1;        // sub-tiles of 64 keys
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int st = 0; st < RING; st++) {
+      mbar_init(kv_full0 + 8 * st, 1);
+      mbar_init(kv_empty0 + 8 * st, 1);
+    }
+    mbar_init(s_full0, 1);
+    mbar_init(s_full0 + 8, 1);
+    mbar_init(p_full, 4);
+    mbar_init(o_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+  const unsigned tmem_s = tmem_base, tmem_o = tmem_base + 2 * SUB;      // S0, S1: 64 columns each; then O
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      mbar_expect_tx(q_full, Q_BYTES);
+      tma_load_2d(q_u, &map_q, head * HD, q_start + tile * BM, q_full);
+    }
+    for (int j = 0; j < n_sub; j++) {
+      const unsigned st = j % RING, round = j / RING;
+      // lanes 0..3: the key boxes of the sub-tile's four granules; lanes 4..7: the value boxes
+      const int key16 = (sub0 + j) * SUB + (lane & 3) * 16;
+      const bool valid = lane < 8 && key16 <= pos_last && key16 + 16 > lo_first;
+      int box_row = 0;
+      if (valid) {
+        const int blk = key16 / pv.page_size;
+        const int page = pv.block_table[(long long)seq_row * pv.bt_stride + blk];
+        box_row = (page * pv.n_kv_heads + kvh) * pv.page_size + (key16 - blk * pv.page_size);
+      }
+      const unsigned n_valid = __popc(__ballot_sync(0xffffffffu, valid));
+      if (lane == 0) {
+        if (round > 0) mbar_wait(kv_empty0 + 8 * st, (round - 1) & 1, status, 41);
+        mbar_expect_tx(kv_full0 + 8 * st, n_valid * BOX_BYTES);
+      }
+      __syncwarp();
+      if (valid)
+        tma_load_2d(kv_u + st * STAGE_BYTES + (lane >> 2) * K_BYTES + (lane & 3) * BOX_BYTES, lane < 4 ? &map_k : &map_v,
+                    0, box_row, kv_full0 + 8 * st);
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ issuer
+    if (lane == 0) {
+      const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(SUB >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+      const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) |
+                                ((unsigned)(BM >> 4) << 24);
+      auto scores = [&](int j) {                   // S[j & 1] = Q K_j^T
+        const unsigned st = j % RING;
+        mbar_wait(kv_full0 + 8 * st, (j / RING) & 1, status, 43);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned k_addr = kv_u + st * STAGE_BYTES;
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++)
+          umma(tmem_s + (unsigned)((j & 1) * SUB), smem_desc(q_u + k * 32), smem_desc(k_addr + k * 32), idesc_qk,
+               k > 0 ? 1u : 0u);
+        umma_commit(s_full0 + 8 * (j & 1));
+      };
+      mbar_wait(q_full, 0, status, 42);
+      scores(0);
+      if (n_sub > 1) scores(1);
+      for (int j = 0; j < n_sub; j++) {
+        const unsigned st = j % RING;
+        mbar_wait(p_full, j & 1, status, 44);          // P_j is in shared memory, S[j & 1] has been read
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned v_addr = kv_u + st * STAGE_BYTES + K_BYTES;
+#pragma unroll
+        for (int k = 0; k < SUB / 16; k++)
+          umma(tmem_o, smem_desc(p_u + k * 32), smem_desc(v_addr + k * 16 * 128), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        umma_commit(kv_empty0 + 8 * st);               // both products of this stage are behind this
+        umma_commit(o_done);
+        if (j + 2 < n_sub) scores(j + 2);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax: a query row per thread
+    const int r = warp * 32 + lane;
+    const unsigned lane_field = (unsigned)(warp * 32) << 16;
+    const int my_pos = pos_first + r;
+    const int my_lo = (window > 0 && my_pos - window + 1 > 0) ? my_pos - window + 1 : 0;
+    const int w_pos_first = pos_first + warp * 32;
+    const int w_lo_last = (window > 0 && w_pos_first + 31 - window + 1 > 0) ? w_pos_first + 31 - window + 1 : 0;
+    const unsigned p_row = p_u + (r >> 3) * 1024 + (r & 7) * 128;
+    float m_row = -INFINITY, l_row = 0.f;
+    for (int j = 0; j < n_sub; j++) {
+      const int key0 = (sub0 + j) * SUB;
+      const unsigned st = j % RING;
+      const unsigned s_addr = tmem_s + lane_field + (unsigned)((j & 1) * SUB);
+      mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, status, 45);
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const bool edge = key0 + SUB - 1 > w_pos_first || key0 < w_lo_last;
+      unsigned sc[2][32];
+      float mx = edge ? row_scores_max<true>(s_addr, sc, key0, my_pos, my_lo)
+                      : row_scores_max<false>(s_addr, sc, key0, my_pos, my_lo);
+      mx *= scale_log2;
+      const float m_cand = fmaxf(m_row, mx);
+      const bool moved = __any_sync(0xffffffffu, m_cand - m_row > MAX_SLACK_LOG2);      // also from -inf
+      const float m_new = moved ? m_cand : m_row;
+      const float m_off = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = !moved ? 1.f : ((m_row == -INFINITY) ? 0.f : ex2(m_row - m_off));
+      if (j > 0) {                                   // O += P V of the sub-tile before: P is free, O is whole
+        mbar_wait(o_done, (j - 1) & 1, status, 46);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        if (moved) {
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; c++) {
+            float v[32];
+            tmem_ld32(tmem_o + lane_field + (unsigned)(c * 32), v);
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] *= alpha;
+            tmem_st32(tmem_o + lane_field + (unsigned)(c * 32), v);
+          }
+        }
+      }
+      if (key0 + SUB - 1 > pos_last || key0 < lo_first) {      // value rows of keys no query may see (thread = key)
+        const int key = key0 + r;
+        if (r < SUB && (key > pos_last || key < lo_first)) {
+          const unsigned row_u = kv_u + st * STAGE_BYTES + K_BYTES + r * 128;
+#pragma unroll
+          for (int c = 0; c < 8; c++) sts128(row_u + c * 16, 0u, 0u, 0u, 0u);
+        }
+      }
+      const float sum = row_probabilities(sc, p_row, r, scale_log2, m_off);
+      l_row = l_row * alpha + sum;
+      m_row = m_new;
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    mbar_wait(o_done, (n_sub - 1) & 1, status, 47);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const float inv = 1.0f / l_row;
+    __nv_bfloat16* orow = out + ((long long)(q_start + tile * BM + r) * n_heads + head) * HD;
+#pragma unroll 1
+    for (int c = 0; c < HD / 32; c++) {
+      float v[32];
+      tmem_ld32(tmem_o + lane_field + (unsigned)(c * 32), v);
+      if (r < rows) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; q4++) {
+          uint4 pk;
+          pk.x = pack_bf16(v[q4 * 8 + 0] * inv, v[q4 * 8 + 1] * inv);
+          pk.y = pack_bf16(v[q4 * 8 + 2] * inv, v[q4 * 8 + 3] * inv);
+          pk.z = pack_bf16(v[q4 * 8 + 4] * inv, v[q4 * 8 + 5] * inv);
+          pk.w = pack_bf16(v[q4 * 8 + 6] * inv, v[q4 * 8 + 7] * inv);
+          *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = pk;
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
+  }
+}
+
+int launch_tc_ahead(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, __nv_bfloat16* out,
+                    const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len, int table_row0, int n_seqs,
+                    int max_q_len, int n_tokens, int n_heads, PagedView pv, float scale, int window, int* status,
+                    cudaStream_t stream) {
+  CUtensorMap mq, mk, mv;
+  int rc = tma_host::bf16_map(q, n_tokens, (long long)n_heads * ahead::HD, BM, 64, &mq);
+  if (rc) return rc;
+  rc = tma_host::bf16_map(k_pool, 1ll << 28, ahead::HD, 16, 64, &mk);
+  if (rc) return rc;
+  rc = tma_host::bf16_map(v_pool, 1ll << 28, ahead::HD, 16, 64, &mv);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_ahead_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)ahead::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(n_heads, (max_q_len + BM - 1) / BM, n_seqs);
+  attn_prefill_tc_ahead_kernel<<<grid, 192, ahead::SMEM, stream>>>(mq, mk, mv, out, seq_q_start, seq_q_len, seq_ctx_len,
+                                                                   table_row0, pv, n_heads, scale * LOG2E, window, status);
+  return (int)cudaGetLastError();
+}
+
 template <int HD, int BN>
 int launch_tc(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, __nv_bfloat16* out,
               const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len, int table_row0, int n_seqs,
@@ -464,19 +706,15 @@ int launch_tc(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bf
   rc = tma_host::bf16_map(v_pool, 1ll << 28, HD, 16, 64, &mv);
   if (rc) return rc;
   const size_t smem = SH::Q_BYTES + STAGES * SH::STAGE_BYTES + SH::P_BYTES + 16 * 8 + 16;
-  // Head size 128 (key tiles of 64: two loads per pass) gains 4 to 6 % from loads that run ahead;
-  // head size 64 (four loads per pass, 168 registers) loses 15 % on a prompt of 2048 and gains 4 % on
-  // one of 8192, so it keeps the serial passes.
-  constexpr bool AHEAD = HD == 128;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, BN, AHEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid(n_heads, (max_q_len + BM - 1) / BM, n_seqs);
-  attn_prefill_tc_kernel<HD, BN, AHEAD><<<grid, 192, smem, stream>>>(mq, mk, mv, out, seq_q_start, seq_q_len, seq_ctx_len,
+  attn_prefill_tc_kernel<HD, BN><<<grid, 192, smem, stream>>>(mq, mk, mv, out, seq_q_start, seq_q_len, seq_ctx_len,
                                                                     table_row0, pv, n_heads, scale * LOG2E, window, status);
   return (int)cudaGetLastError();
 }
@@ -499,8 +737,8 @@ int launch_prefill_tc(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
   if (!g_prefill_tc || pv.page_size % 16 || max_q_len < BM || n_tokens <= 0) return MF_ERR_BAD_ARG;
   if ((((uintptr_t)q | (uintptr_t)out) & 15) != 0) return MF_ERR_BAD_ARG;
   if (pv.head_dim == 64)
-    return launch_tc<64, 128>(q, k_pool, v_pool, out, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs,
-                              max_q_len, n_tokens, n_heads, pv, scale, window, status, stream);
+    return launch_tc_ahead(q, k_pool, v_pool, out, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs, max_q_len,
+                           n_tokens, n_heads, pv, scale, window, status, stream);
   if (pv.head_dim == 128)
     return launch_tc<128, 64>(q, k_pool, v_pool, out, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs,
                               max_q_len, n_tokens, n_heads, pv, scale, window, status, stream);
