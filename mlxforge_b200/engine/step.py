@@ -48,7 +48,8 @@ class StepBatch:
         self.n_seqs = 0
         self.n_wanted = 0
         self.n_decode = 0                 # leading sequences (and tokens) that bring one token
-        self.tokens = None
+        self.tokens = None                # [T] int32, device: where the step's token ids are read
+        self.meta_tokens = None           # the copy of the host's token ids inside the metadata buffer
         self.positions = None
         self.seq_of_token = None
         self.want_rows = None
@@ -130,9 +131,9 @@ class ModelRunner:
         graphed = self.cuda_graphs and all(len(e.tokens) == 1 for e in entries)
         decode_only = all(len(e.tokens) == 1 for e in entries)
         batch = self._build(entries, pad_tables=decode_only)
-        if device_tokens is not None:
-            # after the copy of the metadata, in stream order: one-token entries keep their order
-            batch.tokens.copy_(device_tokens[:len(entries)], non_blocking=True)
+        # one-token entries keep their order, so row r of device_tokens is entry r's token; the
+        # batch object may be last step's (see _advance), so the choice is made afresh every step
+        batch.tokens = device_tokens[:len(entries)] if device_tokens is not None else batch.meta_tokens
         logits = self._forward_graphed(batch) if graphed else self.model.forward(batch, self.cache)
         for e in entries:
             self.cache.commit(e.seq, len(e.tokens))
@@ -146,7 +147,10 @@ class ModelRunner:
         replay needs no host work beyond the one copy of that buffer.  The first step of
         a shape runs eagerly (it sizes the scratch), the second is captured."""
         from ..csrc import binding
-        key = (batch.n_seqs, batch.n_wanted, tuple(t.shape[1] for t in batch._block_tables.values()))
+        # the graph holds the address its tokens come from: the metadata buffer, or the sampler's
+        # output when the step was launched before the host saw the tokens
+        key = (batch.n_seqs, batch.n_wanted, tuple(t.shape[1] for t in batch._block_tables.values()),
+               batch.tokens.data_ptr())
         entry = self._graphs.get(key)
         if entry is not None and entry[0] == (self.rt.generation, self._meta.data_ptr()):
             entry[1].replay()
@@ -290,6 +294,7 @@ class ModelRunner:
         views = [self._meta[off:off + p.size] for p, off in zip(parts, offsets)]
         (b.tokens, b.positions, b.seq_of_token, b.want_rows, b.slots, b.seq_q_start, b.seq_q_len,
          b.seq_ctx_len) = views[:8]
+        b.meta_tokens = b.tokens
         for g, tab in enumerate(tables):
             b._block_tables[g] = views[8 + g].view(tab.shape)
         if pad_tables and self._plain_groups:

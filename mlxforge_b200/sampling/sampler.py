@@ -30,13 +30,20 @@ class Sampler:
         if n <= self._cap:
             return
         self._cap = max(n, 2 * self._cap)
-        self._host = torch.empty((2, self._cap), dtype=torch.float32, pin_memory=True)
+        # per turn, like the tokens' host buffers: a launch writes its rows' temperatures and draws
+        # here while the copy of the launch before it may not have run yet
+        self._host = torch.empty((2, 2, self._cap), dtype=torch.float32, pin_memory=True)
         self._dev = torch.empty((2, self._cap), dtype=torch.float32, device=self.device)
         self._out = torch.empty(self._cap, dtype=torch.int32, device=self.device)
         # two host buffers taken in turn: one launch may be in flight while the one before is read
         self._out_host = [torch.empty(self._cap, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._events = [torch.cuda.Event() for _ in range(2)]
         self._turn = 0
+        # the tokens go to the host on a stream of their own, so that the next step's first copy (its
+        # metadata, host to device) does not queue behind this one
+        self._out_stream = torch.cuda.Stream(device=self.device)
+        self._sampled = torch.cuda.Event()
+        self._last_copy = None            # event of the last copy out of self._out
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], indices: Sequence[int],
                histories: Sequence[Sequence[int]] = ()) -> List[int]:
@@ -70,19 +77,26 @@ class Sampler:
             ops.apply_penalties(logits, params, histories)
         all_greedy = all(p.greedy for p in params)
         out = self._out[:n]
+        main = torch.cuda.current_stream(self.device)
+        if self._last_copy is not None:
+            main.wait_event(self._last_copy)      # the copy before this one has read `out` (long ago)
         if all_greedy:
             ops.sample(logits, None, None, out)
         else:
-            h = self._host.numpy()
+            h = self._host[self._turn].numpy()
             for r, (p, i) in enumerate(zip(params, indices)):
                 h[0, r] = 0.0 if p.greedy else p.temperature
                 h[1, r] = uniform_draw(p.seed, i)
-            self._dev[:, :n].copy_(self._host[:, :n], non_blocking=True)
+            self._dev[:, :n].copy_(self._host[self._turn][:, :n], non_blocking=True)
             if any(p.has_filters and not p.greedy for p in params):
                 ops.filter_logits(logits, params)
             ops.sample(logits, self._dev[0, :n], self._dev[1, :n], out)
         turn = self._turn
         self._turn ^= 1
-        self._out_host[turn][:n].copy_(out, non_blocking=True)
-        self._events[turn].record()
+        self._sampled.record(main)
+        with torch.cuda.stream(self._out_stream):
+            self._out_stream.wait_event(self._sampled)
+            self._out_host[turn][:n].copy_(out, non_blocking=True)
+            self._events[turn].record(self._out_stream)
+        self._last_copy = self._events[turn]
         return (turn, n)

@@ -174,6 +174,28 @@ def test_sample_kernel_against_plain(V):
             assert out[r].item() == tok, (r, tok, out[r].item())
 
 
+def test_two_sampler_launches_in_flight_keep_their_own_draws():
+    """The engine launches a step's sampling before it has collected the step before.  The second
+    launch must not change what the first one reads from the host (its rows' temperatures and
+    uniform draws), even if the first has not started when the second is issued: here the device
+    is kept busy for a while before the first launch, and the two launches draw differently."""
+    import torch
+    import mlxforge_b200 as mf
+    from mlxforge_b200.sampling.sampler import Sampler
+    rng = np.random.default_rng(3)
+    n, V = 5, 4099
+    logits = [torch.from_numpy((rng.standard_normal((n, V)) * 1.5).astype(np.float32)).cuda() for _ in range(2)]
+    params = [mf.SamplingParams(temperature=0.7 + 0.1 * r, seed=11 + r) for r in range(n)]
+    one = Sampler("cuda")
+    want = [one.sample(logits[i].clone(), params, [i * 7 + r for r in range(n)]) for i in range(2)]
+    assert want[0] != want[1]
+    two = Sampler("cuda")
+    torch.cuda._sleep(200_000_000)                  # about a tenth of a second of device time
+    h0 = two.launch(logits[0].clone(), params, [r for r in range(n)])
+    h1 = two.launch(logits[1].clone(), params, [7 + r for r in range(n)])
+    assert [two.collect(h0), two.collect(h1)] == want
+
+
 def test_filters_and_penalties_against_plain():
     import torch
     import mlxforge_b200 as mf
