@@ -355,15 +355,23 @@ int launch_decode(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __n
 
 // attention_decode_tma.cu: the first kernel with keys and values brought in by the TMA unit
 int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
-                      float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv, long long pool_rows,
-                      const int* positions, const int* seq_of_token, float scale, int window, int max_ctx,
-                      int* status, int* split_out, cudaStream_t stream);
+                      __nv_bfloat16* out, float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv,
+                      long long pool_rows, const int* positions, const int* seq_of_token, float scale, int window,
+                      int max_ctx, int* status, int* split_out, int* merged_out, cudaStream_t stream);
+extern int g_merge_inside;
 
 static int g_decode_tma = 1;
 static int* g_decode_status = nullptr;
 
 // Whether head size 64 takes the TMA kernel (default on), and the device word its bounded
 // waits report to (may be null).  Returns the previous on/off setting.
+// 1 (the default): the TMA kernel merges its splits itself; 0: the merge kernel follows it.
+MF_API int mf_set_decode_merge_inside(int on) {
+  const int old = g_merge_inside;
+  g_merge_inside = on ? 1 : 0;
+  return old;
+}
+
 MF_API int mf_set_decode_tma(int on, int* status) {
   const int old = g_decode_tma;
   g_decode_tma = on ? 1 : 0;
@@ -394,9 +402,10 @@ MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_
   __nv_bfloat16* oo = (__nv_bfloat16*)out;
   if (hd == 64 && g_decode_tma) {
     // the map's row count only bounds the unit's own range check; rows beyond the pool are never asked for
-    int split = SPLIT_KEYS;
-    const int rc = launch_decode_tma(qq, kk, vv, part_o, part_ml, n_tokens, n_heads, pv, 1ll << 28, positions,
-                                     seq_of_token, scale, window, max_ctx, g_decode_status, &split, stream);
+    int split = SPLIT_KEYS, merged = 0;
+    const int rc = launch_decode_tma(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, 1ll << 28, positions,
+                                     seq_of_token, scale, window, max_ctx, g_decode_status, &split, &merged, stream);
+    if (rc == 0 && merged) return 0;
     if (rc == 0) {
       const int max_splits = (max_ctx + split - 1) / split;
       dim3 mgrid(n_tokens, n_heads);

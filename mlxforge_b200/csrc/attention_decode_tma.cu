@@ -1,8 +1,10 @@
 // Decode attention for head size 64 with the keys and values brought in by the TMA unit.
 //
 // It computes exactly what attn_decode_kernel (attention_decode.cu) computes and writes the
-// same per-split partial results (same split size, same merge kernel after it), but is built
-// around the memory system instead of around the warps:
+// same per-split partial results, but is built around the memory system instead of around the
+// warps, and it merges its splits itself: the block that finishes the last split of a (token,
+// head group) adds the splits' results in their order and writes the output (see g_tickets).
+// Launches with more groups than there are tickets leave the merge to attn_decode_merge_kernel.
 //   * two persistent blocks per SM walk work items (token, KV head x head group, split of 512
 //     keys), item = block, block + grid, ...;
 //   * a producer warp issues one 2-D tensor copy per granule of 16 keys (a page holds whole
@@ -82,6 +84,14 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CW * 32) : "memory"); }
 
+// One counter per (token, group of heads): every split of that group that saw keys takes a
+// ticket when its partial result is written; the block that draws the last one merges the
+// splits into the output, in the order of the splits, and puts the counter back to zero.
+// Nobody waits for another block.  Launches with more groups than this merge in a kernel of
+// their own (attn_decode_merge_kernel).
+constexpr int MAX_TICKETS = 1 << 16;
+__device__ int g_tickets[MAX_TICKETS];
+
 // What an item is, computed the same way by the producer and the consumers.
 struct Item {
   int t, kvh, head0, n_rows, split, pos, lo, seq, tile0, tile1;
@@ -112,7 +122,7 @@ __device__ __forceinline__ Item make_item(int item, int max_splits, int groups, 
 __global__ void __launch_bounds__((CW + 1) * 32)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __nv_bfloat16* __restrict__ q, float* __restrict__ part_o, float* __restrict__ part_ml,
-                       const int* __restrict__ positions, const int* __restrict__ seq_of_token, PagedView pv,
+                       __nv_bfloat16* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_of_token, PagedView pv,
                        int n_heads, int n_tokens, float scale_log2, int window, int max_splits, int comb_rows,
                        int split_keys, int* __restrict__ status) {
   extern __shared__ unsigned char raw[];
@@ -121,6 +131,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   unsigned char* q_s = smem + STAGES * STAGE_BYTES;                       // [2][16][64] bf16
   float* comb = reinterpret_cast<float*>(q_s + 2 * Q_BYTES);              // [CW][comb_rows][HD + 2]: m, l, o[HD]
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(comb + CW * comb_rows * (HD + 2));
+  int* last_flag = reinterpret_cast<int*>(bars + 2 * STAGES + 4);
   const int CR = comb_rows;              // rows of the combine buffer per warp: the heads of a group
   const unsigned ring_u = smem_u32(ring), q_u = smem_u32(q_s), bars_u = smem_u32(bars);
   const unsigned full0 = bars_u, empty0 = bars_u + 8 * STAGES;
@@ -393,18 +404,52 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         part_ml[row * 2 + 1] = L;
       }
     }
-    consumer_sync();       // `comb` is free for the next item
+    if (out == nullptr) {
+      consumer_sync();     // `comb` is free for the next item
+      continue;
+    }
+    // ---- the ticket; whoever draws the group's last one merges its splits (out != nullptr)
+    __threadfence();       // this thread's part of the partial result, before the ticket
+    consumer_sync();       // also: `comb` is free for the next item
+    const int s0 = w.lo / split_keys, n_live = w.pos / split_keys - s0 + 1;
+    if (threadIdx.x == 0) {
+      const int slot = item / max_splits;
+      const int last = atomicAdd(g_tickets + slot, 1) == n_live - 1;
+      if (last) g_tickets[slot] = 0;
+      *last_flag = last;
+    }
+    consumer_sync();
+    const bool last = *last_flag != 0;
+    consumer_sync();       // everyone has read the flag before the next item writes it
+    if (last) {
+      __threadfence();
+      for (int i = threadIdx.x; i < w.n_rows * HD; i += CW * 32) {
+        const int r = i / HD, d = i - r * HD;
+        const long long row = ((long long)w.t * n_heads + w.head0 + r) * max_splits + s0;
+        float M = -INFINITY;
+        for (int sp = 0; sp < n_live; sp++) M = fmaxf(M, __ldcg(part_ml + (row + sp) * 2));
+        float L = 0.f, acc = 0.f;
+        for (int sp = 0; sp < n_live; sp++) {
+          const float f = exp2f(__ldcg(part_ml + (row + sp) * 2) - M);
+          L += __ldcg(part_ml + (row + sp) * 2 + 1) * f;
+          acc += __ldcg(part_o + (row + sp) * HD + d) * f;
+        }
+        out[((long long)w.t * n_heads + w.head0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
+      }
+    }
   }
 }
 
 }  // namespace
 
+int g_merge_inside = 1;
+
 // Launches the first kernel of the decode attention for head size 64 (the merge kernel of
 // attention_decode.cu follows it).  Returns MF_ERR_BAD_ARG when this path does not apply.
 int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
-                      float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv, long long pool_rows,
-                      const int* positions, const int* seq_of_token, float scale, int window, int max_ctx,
-                      int* status, int* split_out, cudaStream_t stream) {
+                      __nv_bfloat16* out, float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv,
+                      long long pool_rows, const int* positions, const int* seq_of_token, float scale, int window,
+                      int max_ctx, int* status, int* split_out, int* merged_out, cudaStream_t stream) {
   if (pv.head_dim != HD || pv.page_size % 16) return MF_ERR_BAD_ARG;
   CUtensorMap mk, mv;
   int rc = tma_host::bf16_map(k_pool, pool_rows, HD, 16, HD, &mk);
@@ -413,7 +458,7 @@ int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
   if (rc) return rc;
   const int G0 = n_heads / pv.n_kv_heads;
   const int comb_rows = G0 < 16 ? G0 : 16;
-  const size_t smem = (size_t)STAGES * STAGE_BYTES + 2 * Q_BYTES + (size_t)CW * comb_rows * (HD + 2) * 4 + (2 * STAGES + 4) * 8 + 1024;
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 2 * Q_BYTES + (size_t)CW * comb_rows * (HD + 2) * 4 + (2 * STAGES + 4) * 8 + 8 + 1024;
   static bool configured = false;
   static int n_sms = 0;
   if (!configured) {
@@ -438,7 +483,10 @@ int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
   const int max_splits = (max_ctx + split_keys - 1) / split_keys;
   if (n_items > 0x7fffffff) return MF_ERR_BAD_ARG;
   const int grid = n_items < 2 * n_sms ? (int)n_items : 2 * n_sms;
+  // the merge inside this kernel, where the tickets reach (g_merge_inside: for measurements)
+  const bool inside = g_merge_inside && (long long)n_tokens * pv.n_kv_heads * hgroups <= MAX_TICKETS;
+  *merged_out = inside ? 1 : 0;
   return (int)launch_dep(attn_decode_tma_kernel, dim3(grid), dim3((CW + 1) * 32), smem, stream, mk, mv, q, part_o,
-                         part_ml, positions, seq_of_token, pv, n_heads, n_tokens, scale * LOG2E, window, max_splits,
+                         part_ml, inside ? out : (__nv_bfloat16*)nullptr, positions, seq_of_token, pv, n_heads, n_tokens, scale * LOG2E, window, max_splits,
                          comb_rows, split_keys, status);
 }

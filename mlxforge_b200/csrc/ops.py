@@ -222,10 +222,24 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool 
                                  kernel_status(x.device).data_ptr(), _stream()), "gemm_bf16")
 
 
+_DECODE_TMA = True        # the library's defaults, followed by the setters below (for the launch count)
+_MERGE_INSIDE = True
+
+
 def set_decode_tma(on: bool) -> bool:
     """Switch the TMA decode-attention kernel (head size 64) on or off; returns the previous
     setting.  Both kernels write the same partial results."""
+    global _DECODE_TMA
+    _DECODE_TMA = bool(on)
     return bool(library().mf_set_decode_tma(1 if on else 0, kernel_status().data_ptr()))
+
+
+def set_decode_merge_inside(on: bool) -> bool:
+    """Whether the TMA decode-attention kernel merges its splits itself (the block that finishes a
+    group's last split does it) or a merge kernel follows it; returns the previous setting."""
+    global _MERGE_INSIDE
+    _MERGE_INSIDE = bool(on)
+    return bool(library().mf_set_decode_merge_inside(1 if on else 0))
 
 
 def attention_decode_split(head_dim: int) -> int:
@@ -257,11 +271,14 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     need_o, need_ml = attention_decode_scratch(n, n_heads, head_dim, max_ctx)
     if part_o.numel() < need_o or part_ml.numel() < need_ml or part_o.dtype != torch.float32:
         raise KernelError("attention_decode: scratch too small")
+    # head size 64: one kernel that also merges its splits (as long as its tickets reach); else two
+    one_kernel = (head_dim == 64 and _DECODE_TMA and _MERGE_INSIDE and page_size % 16 == 0
+                  and n * n_kv * ((n_heads // n_kv + 15) // 16) <= 65536)
     check(library().mf_attention_decode(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
                                         part_o.data_ptr(), part_ml.data_ptr(), n, n_heads, n_kv, head_dim,
                                         positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
                                         block_table.shape[1], page_size, scale, window, max_ctx, _stream()),
-          "attention_decode", launches=2)
+          "attention_decode", launches=1 if one_kernel else 2)
 
 
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], u: Optional[torch.Tensor],

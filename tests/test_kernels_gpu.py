@@ -200,20 +200,28 @@ def test_attention_generic(case, dtype):
         assert np.max(np.abs(got[i] - want)) < tol, (i, s, p)
 
 
-@pytest.mark.parametrize("tma", [True, False])
-@pytest.mark.parametrize("case", ATTN_CASES + [(32, 8, 64, [2100, 700, 1, 513, 512], 0), (4, 1, 64, [900, 40], 300)])
+@pytest.mark.parametrize("tma", ["tma", "tma, merge kernel", "no tma"])
+@pytest.mark.parametrize("case", ATTN_CASES + [(32, 8, 64, [2100, 700, 1, 513, 512], 0), (4, 1, 64, [900, 40], 300),
+                                               (8, 2, 64, [5000, 4097, 2048, 2049, 300], 0),
+                                               (8, 2, 64, [5000, 2300, 640], 2500)])
 def test_attention_decode(case, tma):
+    """Head size 64 has the TMA kernel, which merges its splits itself (the block that finishes a
+    group's last split; run twice here: the tickets must be back at zero) or leaves them to the
+    merge kernel, and the kernel without tensor copies."""
     import torch
     from mlxforge_b200.csrc import ops
     nh, nkv, hd, lengths, window = case
-    if not tma and hd != 64:
-        pytest.skip("only head size 64 has two kernels")
-    old = ops.set_decode_tma(tma)
+    if tma != "tma" and hd != 64:
+        pytest.skip("only head size 64 has more than one kernel")
+    old = ops.set_decode_tma(tma != "no tma")
+    old_merge = ops.set_decode_merge_inside(tma == "tma")
     try:
-        _attention_decode_case(case)
-        ops.check_kernel_status()
+        for _ in range(2):
+            _attention_decode_case(case)
+            ops.check_kernel_status()
     finally:
         ops.set_decode_tma(old)
+        ops.set_decode_merge_inside(old_merge)
 
 
 def _attention_decode_case(case):
