@@ -88,7 +88,9 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\
 // ticket when its partial result is written; the block that draws the last one merges the
 // splits into the output, in the order of the splits, and puts the counter back to zero.
 // Nobody waits for another block.  Launches with more groups than this merge in a kernel of
-// their own (attn_decode_merge_kernel).
+// their own (attn_decode_merge_kernel).  The counters belong to the device, not to a launch:
+// launches of this kernel on one device must follow one another (one stream, as the engine
+// has it), not run side by side.
 constexpr int MAX_TICKETS = 1 << 16;
 __device__ int g_tickets[MAX_TICKETS];
 
