@@ -26,7 +26,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: the Llama-3.2-1B shape
+# the headline configuration: the Llama-3.2-1B shape
 LLAMA_1B = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 16, "hidden_size": 2048,
     "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192,
@@ -35,7 +35,7 @@ LLAMA_1B = {
                      "original_max_position_embeddings": 8192},
     "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": True,
 }
-# configs[3] and [4]: the other shapes that the reference's benchmark names (--shape, for measurements
+# the other shapes that the reference's benchmark configurations name (--shape, for measurements
 # beside the headline; the default run is the 1B shape)
 LLAMA_3B = dict(LLAMA_1B, num_hidden_layers=28, hidden_size=3072, num_attention_heads=24, head_dim=128)
 LLAMA_8B = dict(LLAMA_1B, num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, head_dim=128,
