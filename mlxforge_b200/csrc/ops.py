@@ -23,7 +23,14 @@ def dtype_code(t: torch.Tensor) -> int:
     raise KernelError(f"tensor dtype {t.dtype} is neither float32 nor bfloat16")
 
 
+# The current stream's handle without building a torch.cuda.Stream object for it (that costs
+# about 15 us a call, and every kernel launch asks): torch's own binding for it, where present.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

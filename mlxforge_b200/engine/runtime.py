@@ -25,6 +25,7 @@ class Runtime:
         self.device = torch.device(device)
         self.precise = dtype == torch.float32
         self._buffers: Dict[str, torch.Tensor] = {}
+        self._views: Dict[tuple, tuple] = {}
         # bumped whenever a scratch buffer moves: captured CUDA graphs hold the old addresses
         self.generation = 0
         # rows every per-token buffer is first made for, so that later, larger steps do not move it
@@ -50,6 +51,11 @@ class Runtime:
         """A contiguous scratch tensor of ``shape``; the storage behind ``name``
         only ever grows, so steady-state steps allocate nothing."""
         dtype = dtype or self.dtype
+        # the same view is asked for step after step: keep it, as long as no buffer has moved
+        vkey = (name, shape, dtype)
+        hit = self._views.get(vkey)
+        if hit is not None and hit[0] == self.generation:
+            return hit[1]
         n = 1
         for s in shape:
             n *= int(s)
@@ -62,7 +68,11 @@ class Runtime:
             buf = torch.empty(max(cap, 1), dtype=dtype, device=self.device)
             self._buffers[key] = buf
             self.generation += 1
-        return buf[:n].view(shape)
+        view = buf[:n].view(shape)
+        if len(self._views) > 8192:
+            self._views.clear()
+        self._views[vkey] = (self.generation, view)
+        return view
 
     # ------------------------------------------------------------------ products
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

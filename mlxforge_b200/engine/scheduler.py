@@ -220,10 +220,15 @@ class Scheduler:
         """``entries`` is a step that has been launched but not committed.  If the step after it
         is bound to be the same requests with one more token each, whatever the launched step
         samples short of an end-of-sequence token (every running request is in it and decoding,
-        nobody waits, nobody is cancelled or would reach its length with the token on its way,
-        and the pages are there), return that step; else None.  A request that does end with the
-        token on its way leaves a row in the returned step whose result ``commit`` drops."""
-        if self.waiting or len(entries) != len(self.running):
+        nobody waits who could be admitted, nobody is cancelled or would reach its length with the
+        token on its way, and the pages are there), return that step; else None.  A request that
+        does end with the token on its way leaves a row in the returned step whose result
+        ``commit`` drops.  With every slot taken a waiting request cannot be admitted before a
+        running one ends, so it does not stand in the way; if a running one meets its EOS with
+        the token on its way, the waiting one gets in one step later than without this."""
+        if self.waiting and len(self.running) < self.cfg.max_running:
+            return None
+        if len(entries) != len(self.running):
             return None
         n_groups = len(self.cache.free_pages())
         taken = [0] * n_groups

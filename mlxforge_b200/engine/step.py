@@ -95,6 +95,7 @@ class ModelRunner:
         self._graphs: Dict[tuple, tuple] = {}
         self._warm: set = set()
         self.graph_replays = 0
+        self._feed: Optional[torch.Tensor] = None     # the last device buffer a step's tokens were fed from
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None
@@ -133,7 +134,16 @@ class ModelRunner:
         batch = self._build(entries, pad_tables=decode_only)
         # one-token entries keep their order, so row r of device_tokens is entry r's token; the
         # batch object may be last step's (see _advance), so the choice is made afresh every step
-        batch.tokens = device_tokens[:len(entries)] if device_tokens is not None else batch.meta_tokens
+        if device_tokens is not None:
+            self._feed = device_tokens
+            batch.tokens = device_tokens[:len(entries)]
+        elif graphed and self._feed is not None and self._feed.numel() >= len(entries):
+            # a caller that feeds some steps on the device gets ONE graph per shape, reading from the
+            # feed buffer: the steps whose tokens come from the host copy them there first
+            batch.tokens = self._feed[:len(entries)]
+            batch.tokens.copy_(batch.meta_tokens, non_blocking=True)
+        else:
+            batch.tokens = batch.meta_tokens
         logits = self._forward_graphed(batch) if graphed else self.model.forward(batch, self.cache)
         for e in entries:
             self.cache.commit(e.seq, len(e.tokens))

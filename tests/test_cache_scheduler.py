@@ -367,6 +367,9 @@ def test_continue_decoding_says_when_the_next_step_is_known():
     c = Request([3] * 4, GREEDY, max_tokens=3)
     s.submit(c)
     assert s.continue_decoding(eng.inflight) is None, "somebody waits: the next step has to be planned"
+    s.cfg.max_running = 2
+    assert s.continue_decoding(eng.inflight) is not None, "somebody waits, but no slot is free before one ends"
+    s.cfg.max_running = 4
     eng.run()
     assert a.output_ids == [tok(a, 10 + i) for i in range(6)] and a.finish_reason == "length"
     assert len(b.output_ids) == 50 and len(c.output_ids) == 3
