@@ -13,6 +13,7 @@ position and sequence index, and a block table per sequence and cache group.
 from __future__ import annotations
 
 import gc
+from collections import OrderedDict
 import weakref
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -92,7 +93,8 @@ class ModelRunner:
         self._last: Optional[dict] = None     # the last decode-only step's metadata, for _advance
         self._plain_groups = all(g.need.window == 0 for g in cache.layout.paged)
         # CUDA graphs of decode-only steps, keyed by the shape of the step's metadata
-        self._graphs: Dict[tuple, tuple] = {}
+        self._graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
+        self.max_graphs = 256
         self._warm: set = set()
         self.graph_replays = 0
         self._feed: Optional[torch.Tensor] = None     # the last device buffer a step's tokens were fed from
@@ -163,6 +165,7 @@ class ModelRunner:
                batch.tokens.data_ptr())
         entry = self._graphs.get(key)
         if entry is not None and entry[0] == (self.rt.generation, self._meta.data_ptr()):
+            self._graphs.move_to_end(key)
             entry[1].replay()
             binding.count_launches(entry[3])
             self.graph_replays += 1
@@ -170,8 +173,9 @@ class ModelRunner:
         if key not in self._warm:
             self._warm.add(key)
             return self.model.forward(batch, self.cache)
-        if len(self._graphs) >= 64:
-            self._graphs.clear()
+        self._graphs.pop(key, None)                  # a graph over buffers that have moved since
+        while len(self._graphs) >= self.max_graphs:
+            self._graphs.popitem(last=False)         # the shape that has not run for the longest time
         graph = torch.cuda.CUDAGraph()
         before = binding.launch_count()
         # Nothing may free device or pinned memory while the stream is capturing (the allocators
