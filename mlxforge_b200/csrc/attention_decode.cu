@@ -361,6 +361,11 @@ int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
 extern int g_merge_inside;
 
 static int g_decode_tma = 1;
+static int g_last_decode_launches = 2;
+
+// How many kernels the last call of mf_attention_decode launched (1: the TMA kernel merged its
+// splits itself; 2: a merge kernel followed).
+MF_API int mf_attention_decode_launches() { return g_last_decode_launches; }
 static int* g_decode_status = nullptr;
 
 // Whether head size 64 takes the TMA kernel (default on), and the device word its bounded
@@ -397,6 +402,7 @@ MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_
   if (hd < 16 || hd > 256 || hd % 16 || n_kv <= 0 || n_heads % n_kv || max_ctx <= 0) return MF_ERR_BAD_ARG;
   if (n_tokens > 65535) return MF_ERR_BAD_ARG;
   PagedView pv{block_table, bt_stride, page_size, n_kv, hd};
+  g_last_decode_launches = 2;
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_pool,
                       *vv = (const __nv_bfloat16*)v_pool;
   __nv_bfloat16* oo = (__nv_bfloat16*)out;
@@ -405,7 +411,10 @@ MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_
     int split = SPLIT_KEYS, merged = 0;
     const int rc = launch_decode_tma(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, 1ll << 28, positions,
                                      seq_of_token, scale, window, max_ctx, g_decode_status, &split, &merged, stream);
-    if (rc == 0 && merged) return 0;
+    if (rc == 0 && merged) {
+      g_last_decode_launches = 1;
+      return 0;
+    }
     if (rc == 0) {
       const int max_splits = (max_ctx + split - 1) / split;
       dim3 mgrid(n_tokens, n_heads);

@@ -30,6 +30,7 @@ _SIGNATURES = {
     "mf_set_pdl": [c_int],
     "mf_set_decode_tma": [c_int, _P],
     "mf_set_decode_merge_inside": [c_int],
+    "mf_attention_decode_launches": [],
     "mf_gemm_bf16": [_P, _P, _P, c_int, c_int, c_int, c_int, _P, _P],
     "mf_stream_max_rows": [],
     "mf_set_stream_tensor_copies": [c_int],

@@ -10,7 +10,7 @@ from typing import Optional
 
 import torch
 
-from .binding import KernelError, check, library
+from .binding import KernelError, check, count_launches, library
 
 F32, BF16 = 0, 1
 
@@ -229,23 +229,15 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool 
                                  kernel_status(x.device).data_ptr(), _stream()), "gemm_bf16")
 
 
-_DECODE_TMA = True        # the library's defaults, followed by the setters below (for the launch count)
-_MERGE_INSIDE = True
-
-
 def set_decode_tma(on: bool) -> bool:
     """Switch the TMA decode-attention kernel (head size 64) on or off; returns the previous
     setting.  Both kernels write the same partial results."""
-    global _DECODE_TMA
-    _DECODE_TMA = bool(on)
     return bool(library().mf_set_decode_tma(1 if on else 0, kernel_status().data_ptr()))
 
 
 def set_decode_merge_inside(on: bool) -> bool:
     """Whether the TMA decode-attention kernel merges its splits itself (the block that finishes a
     group's last split does it) or a merge kernel follows it; returns the previous setting."""
-    global _MERGE_INSIDE
-    _MERGE_INSIDE = bool(on)
     return bool(library().mf_set_decode_merge_inside(1 if on else 0))
 
 
@@ -278,14 +270,13 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     need_o, need_ml = attention_decode_scratch(n, n_heads, head_dim, max_ctx)
     if part_o.numel() < need_o or part_ml.numel() < need_ml or part_o.dtype != torch.float32:
         raise KernelError("attention_decode: scratch too small")
-    # head size 64: one kernel that also merges its splits (as long as its tickets reach); else two
-    one_kernel = (head_dim == 64 and _DECODE_TMA and _MERGE_INSIDE and page_size % 16 == 0
-                  and n * n_kv * ((n_heads // n_kv + 15) // 16) <= 65536)
     check(library().mf_attention_decode(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
                                         part_o.data_ptr(), part_ml.data_ptr(), n, n_heads, n_kv, head_dim,
                                         positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
                                         block_table.shape[1], page_size, scale, window, max_ctx, _stream()),
-          "attention_decode", launches=1 if one_kernel else 2)
+          "attention_decode", launches=0)
+    # one kernel when the TMA kernel merged its splits itself, two when a merge kernel followed
+    count_launches(int(library().mf_attention_decode_launches()))
 
 
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], u: Optional[torch.Tensor],

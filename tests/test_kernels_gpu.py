@@ -203,7 +203,9 @@ def test_attention_generic(case, dtype):
 @pytest.mark.parametrize("tma", ["tma", "tma, merge kernel", "no tma"])
 @pytest.mark.parametrize("case", ATTN_CASES + [(32, 8, 64, [2100, 700, 1, 513, 512], 0), (4, 1, 64, [900, 40], 300),
                                                (8, 2, 64, [5000, 4097, 2048, 2049, 300], 0),
-                                               (8, 2, 64, [5000, 2300, 640], 2500)])
+                                               (8, 2, 64, [5000, 2300, 640], 2500),
+                                               (8, 8, 64, [600 + 7 * i for i in range(30)], 0),    # two items to a block
+                                               (8, 8, 64, [600 + 7 * i for i in range(44)], 0)])   # more: merge kernel
 def test_attention_decode(case, tma):
     """Head size 64 has the TMA kernel, which merges its splits itself (the block that finishes a
     group's last split; run twice here: the tickets must be back at zero) or leaves them to the
