@@ -425,3 +425,24 @@ def test_pipelined_random_load_matches_the_plain_loop(seed):
         assert m.free_pages() == m.total_pages()
         results.append([(r.output_ids, r.finish_reason) for r in reqs])
     assert results[0] == results[1]
+
+
+def test_scratch_views_are_kept_until_a_buffer_moves():
+    """The runtime hands out the same view for the same (name, shape) step after step, and a view
+    made before a buffer grew is never handed out again (captured graphs are rebuilt on the same
+    signal, ``generation``)."""
+    import torch
+    from mlxforge_b200.engine.runtime import Runtime
+    rt = Runtime(torch.float32, device="cpu")
+    a = rt.buffer("x", (4, 8))
+    assert rt.buffer("x", (4, 8)) is a and rt.generation == 1
+    other = rt.buffer("y", (3,), torch.int32)
+    assert other.dtype == torch.int32 and rt.generation == 2
+    assert rt.buffer("x", (4, 8)).data_ptr() == a.data_ptr(), "y's arrival moved nothing of x"
+    big = rt.buffer("x", (16, 8))                      # x grows: its storage moves
+    assert rt.generation == 3
+    again = rt.buffer("x", (4, 8))
+    assert again is not a and again.data_ptr() == big.data_ptr()
+    rt.reserve_rows = 64
+    wide = rt.buffer("z", (2, 5))
+    assert rt.buffer("z", (64, 5)).data_ptr() == wide.data_ptr(), "made for reserve_rows rows at once"
