@@ -207,3 +207,33 @@ def test_random_weights_mode_roundtrip(tmp_path):
     _, w3 = P.load_model_dir(d3)
     assert not np.array_equal(w3["model.norm.weight"], n[:0]) and np.all(w3["model.norm.weight"] == 1.0)
     assert not np.allclose(w3["model.embed_tokens.weight"], w["model.embed_tokens.weight"])
+
+
+def test_command_line_without_a_gpu(tmp_path):
+    """The commands that need no device work on the CPU (random-weights writes a model folder,
+    dump-weights lists it as ``key [shape] dtype``, apps/mlxforge_cli.cpp:147-191); generate says
+    loudly that there is no device instead of computing anything on the CPU."""
+    import json
+    import subprocess
+    import sys
+    import torch
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 48,
+           "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 16, "intermediate_size": 80,
+           "vocab_size": 101, "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False}
+    (tmp_path / "cfg.json").write_text(json.dumps(cfg))
+
+    def run(*args):
+        return subprocess.run([sys.executable, "-m", "mlxforge_b200", *args], capture_output=True, text=True, cwd=root)
+
+    r = run("random-weights", str(tmp_path / "cfg.json"), str(tmp_path / "m"), "--seed", "3")
+    assert r.returncode == 0, r.stderr
+    assert sorted(os.listdir(tmp_path / "m")) == ["config.json", "model.safetensors"]
+    r = run("dump-weights", str(tmp_path / "m"))
+    assert r.returncode == 0, r.stderr
+    lines = r.stdout.splitlines()
+    assert "lm_head.weight [101, 48] BF16" in lines and "model.layers.1.self_attn.k_proj.weight [16, 48] BF16" in lines
+    assert len([l for l in lines if l.endswith("BF16")]) == 2 * 9 + 3      # nine per layer, embedding, norm, head
+    if not torch.cuda.is_available():
+        r = run("generate", str(tmp_path / "m"), "1,2,3", "4")
+        assert r.returncode != 0 and "no CPU fallback" in r.stderr
