@@ -275,6 +275,21 @@ class LlamaConfig(ModelConfig):
         return j
 
 
+def apply_rope_scaling_override(j: Dict[str, Any], text: str) -> Dict[str, Any]:
+    """``j`` with its ``rope_scaling`` replaced wholesale by the JSON object in ``text`` (a full
+    replacement, not a merge; src/core/config.cpp:282-300).  The type is validated when the
+    result is parsed."""
+    try:
+        o = json.loads(text)
+    except json.JSONDecodeError as e:
+        raise ConfigError(f"invalid rope_scaling override JSON: {e}")
+    if not isinstance(o, dict):
+        raise ConfigError('rope_scaling override must be a JSON object, e.g. {"rope_type":"linear","factor":4.0}')
+    j = dict(j)
+    j["rope_scaling"] = o
+    return j
+
+
 def read_config_json(path: str) -> Dict[str, Any]:
     """Read ``config.json`` (a file, or the folder holding it) with the
     reference's file errors (src/core/config.cpp:232-244)."""

@@ -332,16 +332,20 @@ int launch_decode(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __n
   const size_t stage = (size_t)(16 * ld + NSTAGE * WARPS * 2 * KPW * ld) * sizeof(__nv_bfloat16);
   const size_t combine = (size_t)16 * ld * sizeof(__nv_bfloat16) + (size_t)WARPS * 16 * (10 + hd) * sizeof(float);
   const size_t smem = stage > combine ? stage : combine;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce once;
+  const int dev_ = mf_current_device();
+  if (dev_ < 0) return MF_ERR_BAD_ARG;
+  if (!once.done[dev_]) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          200 * 1024);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(attn_decode_kernel<HD_MAX>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    once.done[dev_] = true;
   }
   dim3 grid(max_splits, pv.n_kv_heads * hgroups, n_tokens);
+  mf_count(MF_K_ATTN_DECODE);
+  mf_count(MF_K_ATTN_DECODE_MERGE);
   cudaError_t e = launch_dep(attn_decode_kernel<HD_MAX>, grid, dim3(WARPS * 32), smem, stream, q, k_pool, v_pool,
                              part_o, part_ml, positions, seq_of_token, pv, n_heads, scale * LOG2E, window, max_splits);
   if (e != cudaSuccess) return (int)e;
@@ -412,10 +416,13 @@ MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_
     const int rc = launch_decode_tma(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, 1ll << 28, positions,
                                      seq_of_token, scale, window, max_ctx, g_decode_status, &split, &merged, stream);
     if (rc == 0 && merged) {
+      mf_count(MF_K_ATTN_DECODE_TMA_MERGED);
       g_last_decode_launches = 1;
       return 0;
     }
     if (rc == 0) {
+      mf_count(MF_K_ATTN_DECODE_TMA);
+      mf_count(MF_K_ATTN_DECODE_MERGE);
       const int max_splits = (max_ctx + split - 1) / split;
       dim3 mgrid(n_tokens, n_heads);
       return (int)launch_dep(attn_decode_merge_kernel, mgrid, dim3(64), 0, stream, (const float*)part_o,

@@ -29,7 +29,11 @@
 // Nothing in it has to start at zero: every partial result that the merge kernel reads was written
 // by the first kernel of the same call.  Two calls that can run on the GPU at the same time
 // (different streams with no ordering between them) race on the array and both results are then
-// undefined: order them on one stream or with events.
+// undefined: order them on one stream or with events.  For head size 64 the same holds between
+// this entry point and the ordinary mf_attention_decode, even when that one has scratch of its
+// own: the kernel that both launch counts the finished splits of every (token, head group) in a
+// table of tickets that is one per device (g_tickets, attention_decode_tma.cu), so ALL decode
+// attention calls of head size 64 on a device must be ordered one after the other.
 //
 // It calls no cudaMalloc, cudaFree or allocating library routine.  Arguments are those of
 // mf_attention_decode without the two scratch pointers, plus `err`/`err_len`, an optional buffer

@@ -461,16 +461,14 @@ int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
   const int G0 = n_heads / pv.n_kv_heads;
   const int comb_rows = G0 < 16 ? G0 : 16;
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 2 * Q_BYTES + (size_t)CW * comb_rows * (HD + 2) * 4 + (2 * STAGES + 4) * 8 + 8 + 1024;
-  static bool configured = false;
-  static int n_sms = 0;
-  if (!configured) {
+  static DeviceOnce once;
+  const int dev_ = mf_current_device();
+  const int n_sms = mf_sm_count();
+  if (dev_ < 0 || n_sms <= 0) return MF_ERR_BAD_ARG;
+  if (!once.done[dev_]) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
-    int dev = 0;
-    e = cudaGetDevice(&dev);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
+    once.done[dev_] = true;
   }
   // Longer splits cost less per key (an item ends with a combine of the eight warps), shorter
   // ones give more items: take the longest split that still gives most blocks an item.
@@ -495,4 +493,14 @@ int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
   return (int)launch_dep(attn_decode_tma_kernel, dim3(grid), dim3((CW + 1) * 32), smem, stream, mk, mv, q, part_o,
                          part_ml, inside ? out : (__nv_bfloat16*)nullptr, positions, seq_of_token, pv, n_heads, n_tokens, scale * LOG2E, window, max_splits,
                          comb_rows, split_keys, status);
+}
+
+// After a kernel of this file gave up a bounded wait its tickets may be left counting: the next
+// launch's merges would then fire at the wrong split or never.  This puts every ticket back to
+// zero (on `stream`, ordered like any launch).
+MF_API int mf_reset_decode_tickets(cudaStream_t stream) {
+  void* p = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&p, g_tickets);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemsetAsync(p, 0, sizeof(int) * MAX_TICKETS, stream);
 }

@@ -80,6 +80,7 @@ MF_API int mf_attention_generic(const void* q, const void* k_pool, const void* v
   PagedView pv{block_table, bt_stride, page_size, n_kv, hd};
   dim3 grid(T, n_heads);
   const size_t smem = (size_t)(hd + CHUNK) * sizeof(float);
+  if (dtype == MF_F32 || dtype == MF_BF16) mf_count(MF_K_ATTN_GENERIC);
   if (dtype == MF_F32)
     attention_generic_kernel<float><<<grid, CHUNK, smem, stream>>>(
         (const float*)q, (const float*)k_pool, (const float*)v_pool, (float*)out, positions, seq_of_token, pv,

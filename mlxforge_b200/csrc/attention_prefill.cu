@@ -289,16 +289,19 @@ int launch_prefill(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __
   constexpr int BM = WARPS * 16 * Shape<HD_MAX>::MT;
   const int ld = pv.head_dim + 8;
   const size_t smem = (size_t)(BM * ld + 4 * BN * ld) * sizeof(__nv_bfloat16);
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce once;
+  const int dev_ = mf_current_device();
+  if (dev_ < 0) return MF_ERR_BAD_ARG;
+  if (!once.done[dev_]) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          200 * 1024);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(attn_prefill_kernel<HD_MAX>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    once.done[dev_] = true;
   }
   dim3 grid(n_heads, (max_q_len + BM - 1) / BM, n_seqs);
+  mf_count(MF_K_ATTN_PREFILL_MMA);
   attn_prefill_kernel<HD_MAX><<<grid, WARPS * 32, smem, stream>>>(q, k_pool, v_pool, out, seq_q_start, seq_q_len,
                                                                  seq_ctx_len, table_row0, pv, n_heads,
                                                                  scale * LOG2E, window);

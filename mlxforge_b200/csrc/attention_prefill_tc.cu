@@ -678,14 +678,17 @@ int launch_tc_ahead(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const _
   if (rc) return rc;
   rc = tma_host::bf16_map(v_pool, 1ll << 28, ahead::HD, 16, 64, &mv);
   if (rc) return rc;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce once;
+  const int dev_ = mf_current_device();
+  if (dev_ < 0) return MF_ERR_BAD_ARG;
+  if (!once.done[dev_]) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_ahead_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)ahead::SMEM);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    once.done[dev_] = true;
   }
   dim3 grid(n_heads, (max_q_len + BM - 1) / BM, n_seqs);
+  mf_count(MF_K_ATTN_PREFILL_TC);
   attn_prefill_tc_ahead_kernel<<<grid, 192, ahead::SMEM, stream>>>(mq, mk, mv, out, seq_q_start, seq_q_len, seq_ctx_len,
                                                                    table_row0, pv, n_heads, scale * LOG2E, window, status);
   return (int)cudaGetLastError();
@@ -706,14 +709,17 @@ int launch_tc(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bf
   rc = tma_host::bf16_map(v_pool, 1ll << 28, HD, 16, 64, &mv);
   if (rc) return rc;
   const size_t smem = SH::Q_BYTES + STAGES * SH::STAGE_BYTES + SH::P_BYTES + 16 * 8 + 16;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce once;
+  const int dev_ = mf_current_device();
+  if (dev_ < 0) return MF_ERR_BAD_ARG;
+  if (!once.done[dev_]) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    once.done[dev_] = true;
   }
   dim3 grid(n_heads, (max_q_len + BM - 1) / BM, n_seqs);
+  mf_count(MF_K_ATTN_PREFILL_TC);
   attn_prefill_tc_kernel<HD, BN><<<grid, 192, smem, stream>>>(mq, mk, mv, out, seq_q_start, seq_q_len, seq_ctx_len,
                                                                     table_row0, pv, n_heads, scale * LOG2E, window, status);
   return (int)cudaGetLastError();

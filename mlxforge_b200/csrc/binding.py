@@ -45,6 +45,8 @@ _SIGNATURES = {
                             c_float, c_int, c_int, _P],
     "mf_apply_penalties": [_P, c_int, c_longlong, _P, _P, _P, _P, _P, _P, _P],
     "mf_filter_logits": [_P, c_int, c_int, c_longlong, _P, _P, _P, _P, _P],
+    "mf_kernel_kinds": [],
+    "mf_reset_decode_tickets": [_P],
 }
 
 MF_ERRORS = {10001: "a size or option this kernel does not take", 10002: "an unsupported dtype"}
@@ -67,6 +69,10 @@ def library() -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.argtypes = args
             fn.restype = c_int
+        lib.mf_kernel_name.argtypes = [c_int]
+        lib.mf_kernel_name.restype = ctypes.c_char_p
+        lib.mf_kernel_launches.argtypes = [c_int]
+        lib.mf_kernel_launches.restype = c_longlong
         _LIB = lib
     return _LIB
 
@@ -93,6 +99,14 @@ def launch_count() -> int:
 def count_launches(n: int) -> None:
     global _LAUNCHES
     _LAUNCHES += n
+
+
+def kernel_launches() -> dict:
+    """How often each kind of kernel has been launched by this process, by name (a launch
+    recorded into a CUDA graph counts once, its replays do not).  Tests of whole models use
+    the difference of two readings to say which kernels a model's steps went through."""
+    lib = library()
+    return {lib.mf_kernel_name(i).decode(): int(lib.mf_kernel_launches(i)) for i in range(lib.mf_kernel_kinds())}
 
 
 def check(code: int, what: str, launches: int = 1) -> None:

@@ -100,6 +100,45 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\
 
 extern int g_mf_pdl;      // 1: launch with the dependent-launch attribute (set by mf_set_pdl)
 
+// ---------------------------------------------------------------------------- per-device set-up
+// cudaFuncSetAttribute and the SM count belong to a device, not to the process: a launcher keeps
+// one flag per device ordinal (a function-local `static DeviceOnce`) and asks which device is
+// current.  Ordinals beyond the table are refused by the launcher (MF_ERR_BAD_ARG).
+#define MF_MAX_DEVICES 64
+struct DeviceOnce {
+  bool done[MF_MAX_DEVICES] = {};
+};
+inline int mf_current_device() {
+  int d = -1;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= MF_MAX_DEVICES) return -1;
+  return d;
+}
+// SMs of the current device (looked up once per device); 0 if it cannot be had
+int mf_sm_count();
+
+// ---------------------------------------------------------------------------- which kernels ran
+// Every launcher counts the kernel it launches (also while a stream is capturing), so that a test
+// of a whole model can say which kernels its steps went through: mf_kernel_launches(id).
+enum MfKernel {
+  MF_K_STREAM_ROWS = 0,       // few-row product, row-segment copies
+  MF_K_STREAM_TMAP,           // few-row product, one tensor copy per stage
+  MF_K_SKINNY,                // few-row product without the copy engine (<= 32 rows)
+  MF_K_MID_ROWS,              // product of 17..128 rows (tcgen05, weights on the M side)
+  MF_K_GEMM_TC,               // many-row product, tcgen05
+  MF_K_GEMM_TC_SWIGLU,        // the same with the gated epilogue
+  MF_K_GEMM_F32,
+  MF_K_ATTN_GENERIC,
+  MF_K_ATTN_PREFILL_MMA,
+  MF_K_ATTN_PREFILL_TC,
+  MF_K_ATTN_DECODE,           // split-key decode attention without tensor copies
+  MF_K_ATTN_DECODE_TMA,       // with tensor copies, a merge kernel after it
+  MF_K_ATTN_DECODE_TMA_MERGED,  // with tensor copies, merging its splits itself
+  MF_K_ATTN_DECODE_MERGE,
+  MF_K_COUNT
+};
+extern unsigned long long g_mf_kernel_launches[MF_K_COUNT];
+inline void mf_count(MfKernel k) { g_mf_kernel_launches[k]++; }
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args... args) {

@@ -70,6 +70,7 @@ MF_API int mf_gemm_f32(const float* A, const float* W, float* C, int M, int N, i
   if (K <= 0) return MF_ERR_BAD_ARG;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return MF_ERR_BAD_ARG;
+  mf_count(MF_K_GEMM_F32);
   gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, C, M, N, K, accumulate);
   return (int)cudaGetLastError();
 }

@@ -265,20 +265,18 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int* stat
   rc = tma_host::bf16_map(W, N, K, BN, BK, &mw);
   if (rc) return rc;
   const size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce once;
+  const int dev_ = mf_current_device();
+  if (dev_ < 0) return MF_ERR_BAD_ARG;
+  if (!once.done[dev_]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    once.done[dev_] = true;
   }
-  static int n_sms = 0;
-  if (n_sms == 0) {
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return (int)e;
-  }
+  const int n_sms = mf_sm_count();
+  if (n_sms <= 0) return MF_ERR_BAD_ARG;
   const int n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  mf_count(EPI == 2 ? MF_K_GEMM_TC_SWIGLU : MF_K_GEMM_TC);
   gemm_kernel<BN, EPI><<<n_tiles < n_sms ? n_tiles : n_sms, 192, smem, stream>>>(ma, mw, C, M, N, K, status);
   return (int)cudaGetLastError();
 }

@@ -146,6 +146,7 @@ int launch(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, int
            cudaStream_t stream) {
   // few output rows: halve the tile so that there are enough blocks for every SM
   const bool small = mode == 0 && (N + 15) / 16 < 296;
+  mf_count(MF_K_SKINNY);
   if (small)
     return (int)launch_dep(skinny_kernel<NB, 8, OutT>, dim3((N + 7) / 8), dim3(WARPS * 32), 0, stream, x, W, out, M, N,
                            K, mode);

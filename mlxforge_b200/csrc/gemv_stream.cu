@@ -360,12 +360,14 @@ template <int NB, int ROWS, int T_STAGES, typename OutT>
 int launch_tmap(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int mode, int* status,
                 int n_sms, cudaStream_t stream) {
   const size_t smem = 1024 + (size_t)T_STAGES * T_STAGE_BYTES + 2 * T_STAGES * 8 + (size_t)CW * ROWS * (NB * 8 + 1) * 4;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce once;
+  const int dev_ = mf_current_device();
+  if (dev_ < 0) return MF_ERR_BAD_ARG;
+  if (!once.done[dev_]) {
     cudaError_t e = cudaFuncSetAttribute(stream_tmap_kernel<NB, ROWS, T_STAGES, OutT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    once.done[dev_] = true;
   }
   CUtensorMap map;
   const int rc = tma_host::bf16_map_chunked(W, N, K, ROWS, 128 / ROWS, &map);
@@ -375,6 +377,7 @@ int launch_tmap(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M
   // 296 block slots are four rounds either way, and 256 blocks of four tiles end together
   const int rounds = (n_tiles + 2 * n_sms - 1) / (2 * n_sms);
   const int grid = (n_tiles + rounds - 1) / rounds;
+  mf_count(MF_K_STREAM_TMAP);
   return (int)launch_dep(stream_tmap_kernel<NB, ROWS, T_STAGES, OutT>, dim3(grid), dim3((CW + 1) * 32), smem, stream, x, map,
                          out, M, N, K, mode, status);
 }
@@ -384,16 +387,19 @@ int launch_one(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M,
                int n_sms, cudaStream_t stream) {
   constexpr int STAGES = Ring<ROWS>::STAGES;
   const size_t smem = (size_t)STAGES * ROWS * ROW_BYTES + 2 * STAGES * 8 + (size_t)CW * ROWS * (NB * 8 + 1) * 4;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce once;
+  const int dev_ = mf_current_device();
+  if (dev_ < 0) return MF_ERR_BAD_ARG;
+  if (!once.done[dev_]) {
     cudaError_t e = cudaFuncSetAttribute(stream_kernel<NB, ROWS, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);   // smem depends on the template arguments only
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    once.done[dev_] = true;
   }
   const int n_tiles = (N + ROWS - 1) / ROWS;
   // two blocks per SM
   const int grid = n_tiles < 2 * n_sms ? n_tiles : 2 * n_sms;
+  mf_count(MF_K_STREAM_ROWS);
   return (int)launch_dep(stream_kernel<NB, ROWS, OutT>, dim3(grid), dim3((CW + 1) * 32), smem, stream, x, W, out, M,
                          N, K, mode, status);
 }
@@ -401,13 +407,8 @@ int launch_one(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M,
 template <typename OutT>
 int dispatch(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int mode, int* status,
              cudaStream_t stream) {
-  static int n_sms = 0;
-  if (n_sms == 0) {
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return (int)e;
-  }
+  const int n_sms = mf_sm_count();
+  if (n_sms <= 0) return MF_ERR_BAD_ARG;
   // few output rows: tiles of 8 rows, so that there are blocks for every SM
   const bool small = mode == 0 && (N + 15) / 16 < 2 * n_sms;
   // Tensor copies only where every box lies inside the matrix along K (a whole number of

@@ -170,13 +170,23 @@ def kernel_status(device=None) -> torch.Tensor:
     return t
 
 
+def kernel_gave_up(code: int, device=None) -> KernelError:
+    """What to do when the status word read ``code`` != 0: a kernel with bounded waits gave up,
+    so what it wrote is not to be trusted.  Clears the word and everything such a kernel may
+    have left half done (the decode-attention tickets), and returns the error to raise."""
+    kernel_status(device).zero_()
+    check(library().mf_reset_decode_tickets(_stream()), "reset_decode_tickets", launches=0)
+    return KernelError(f"a kernel's bounded wait ran out (code {code}: 1 = copy producer, 2 = consumer); "
+                       "the results of the step are invalid")
+
+
 def check_kernel_status() -> None:
-    """Raise if a kernel gave up a bounded wait since the last check (reads the word back)."""
-    for t in _STATUS.values():
+    """Raise if a kernel gave up a bounded wait since the last check (reads the word back, which
+    waits for the device: call it where the host waits anyway)."""
+    for key, t in _STATUS.items():
         code = int(t.item())
         if code:
-            t.zero_()
-            raise KernelError(f"a kernel's bounded wait ran out (code {code}: 1 = copy producer, 2 = consumer)")
+            raise kernel_gave_up(code, torch.device("cuda", key))
 
 
 def stream_max_rows() -> int:

@@ -98,11 +98,28 @@ class Engine:
         tokens = max(tokens, config.kv_block_size)
         self.cache = CacheManager(self.model.cache_layout, page_size=config.kv_block_size, max_tokens=tokens,
                                   max_seqs=config.max_running, dtype=dtype, device=str(rt.device))
-        self.runner = ModelRunner(self.model, self.cache, rt, cuda_graphs=config.cuda_graphs)
+        self._assemble(ModelRunner(self.model, self.cache, rt, cuda_graphs=config.cuda_graphs), Sampler(rt.device),
+                       rt.device.index if rt.device.index is not None else torch.cuda.current_device())
+
+    @classmethod
+    def from_parts(cls, config: EngineConfig, model, cache, runner, sampler, device_index: int = 0) -> "Engine":
+        """An engine around parts that already exist: ``model`` needs ``spec.vocab_size`` and
+        ``spec.eos_token_ids``; ``runner.step(entries, device_tokens=None)`` returns what
+        ``sampler.launch`` takes; ``sampler`` has ``launch``, ``collect`` and ``device_ids``.
+        Nothing is loaded.  Tests drive the loop below with stand-ins this way."""
+        self = cls.__new__(cls)
+        self.config = config
+        self.model, self.model_config, self.cache = model, None, cache
+        self._assemble(runner, sampler, device_index)
+        return self
+
+    def _assemble(self, runner, sampler, device_index: int) -> None:
+        config = self.config
+        self.runner = runner
         self.scheduler = Scheduler(self.cache, SchedulerConfig(
             max_running=config.max_running, max_waiting=config.max_waiting,
             token_budget=config.token_budget, prefill_chunk=config.prefill_chunk))
-        self.sampler = Sampler(rt.device)
+        self.sampler = sampler
         self._lock = threading.Lock()
         self._wake = threading.Condition(self._lock)
         self._thread: Optional[threading.Thread] = None
@@ -112,7 +129,7 @@ class Engine:
         self._inflight = None
         self.pipeline = bool(config.pipeline)
         self.steps_ahead = 0              # steps launched before the tokens of the step before were known
-        self._device_index = rt.device.index if rt.device.index is not None else torch.cuda.current_device()
+        self._device_index = device_index
 
     # ------------------------------------------------------------------ submit
     @property

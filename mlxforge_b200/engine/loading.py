@@ -9,9 +9,7 @@ from typing import Tuple
 
 import torch
 
-import json
-
-from ..config.model_config import ConfigError, read_config_json
+from ..config.model_config import apply_rope_scaling_override, read_config_json
 from ..config.registry import config_from_json, get_architecture
 from ..models.decoder import DecoderModel
 from .runtime import Runtime
@@ -44,14 +42,7 @@ def load_model(model_dir: str, dtype="bfloat16", device: str = "cuda",
     library()      # build or load the kernels now: fail before any weight is read
     j = read_config_json(model_dir)
     if rope_scaling:
-        try:
-            o = json.loads(rope_scaling)
-        except json.JSONDecodeError as e:
-            raise ConfigError(f"invalid rope_scaling override JSON: {e}")
-        if not isinstance(o, dict):
-            raise ConfigError('rope_scaling override must be a JSON object, e.g. {"rope_type":"linear","factor":4.0}')
-        j = dict(j)
-        j["rope_scaling"] = o
+        j = apply_rope_scaling_override(j, rope_scaling)
     config = config_from_json(j)
     arch = get_architecture(config.architecture)
     rt = Runtime(parse_dtype(dtype), device)

@@ -24,6 +24,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
+from ..csrc import ops
 from .loading import load_model, parse_dtype
 from .step import ModelRunner, StepEntry
 
@@ -59,6 +60,7 @@ def replay(runner: ModelRunner, lines: IO[str], out_dir: str, done: IO[str] = sy
         logits = runner.step(entries)
         if logits is not None:
             arr = logits.detach().to("cpu", torch.float32).numpy().astype("<f4", copy=False)
+            ops.check_kernel_status()       # the copy has waited for the step: a kernel that gave up shows now
             arr.tofile(os.path.join(out_dir, f"{step}.f32"))
         for rid in rec.get("end", []):
             seq = live.pop(str(rid), None)
@@ -66,6 +68,7 @@ def replay(runner: ModelRunner, lines: IO[str], out_dir: str, done: IO[str] = sy
                 runner.cache.close(seq)
         done.write(f"done {step}\n")
         done.flush()
+    ops.check_kernel_status()
 
 
 def main(argv=None) -> int:

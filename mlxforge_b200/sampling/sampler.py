@@ -37,6 +37,9 @@ class Sampler:
         self._out = torch.empty(self._cap, dtype=torch.int32, device=self.device)
         # two host buffers taken in turn: one launch may be in flight while the one before is read
         self._out_host = [torch.empty(self._cap, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        # the word in which kernels with bounded waits say that one gave up travels with the tokens
+        self._status = ops.kernel_status(self.device)
+        self._status_host = [torch.zeros(1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._events = [torch.cuda.Event() for _ in range(2)]
         self._turn = 0
         # the tokens go to the host on a stream of their own, so that the next step's first copy (its
@@ -63,6 +66,9 @@ class Sampler:
             return []
         turn, n = handle
         self._events[turn].synchronize()
+        code = int(self._status_host[turn][0])
+        if code:
+            raise ops.kernel_gave_up(code, self.device)
         return self._out_host[turn][:n].tolist()
 
     def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], indices: Sequence[int],
@@ -97,6 +103,7 @@ class Sampler:
         with torch.cuda.stream(self._out_stream):
             self._out_stream.wait_event(self._sampled)
             self._out_host[turn][:n].copy_(out, non_blocking=True)
+            self._status_host[turn].copy_(self._status, non_blocking=True)
             self._events[turn].record(self._out_stream)
         self._last_copy = self._events[turn]
         return (turn, n)

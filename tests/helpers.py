@@ -40,9 +40,38 @@ TINY_D = {   # a width, an intermediate size and a vocabulary that are no multip
     "head_dim": 16, "intermediate_size": 52, "vocab_size": 131, "rope_theta": 20000.0,
     "max_position_embeddings": 256, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
 }
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
-SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
-NORM_STD = {"A": 0.0, "B": 0.1, "C": 0.2, "D": 0.05}
+# The two below are still small, but have the shapes that the serving kernels are written for, so
+# that those kernels run inside a model: head size 64 (decode attention with tensor copies, the
+# tcgen05 prefill attention two tiles ahead), widths that are whole stages of the few-row product
+# (one tensor copy per stage), an intermediate size of at least 256 rows' worth of tcgen05 tiles.
+SMALL_E = {  # head_dim 64, GQA 8:2, llama3 scaling, tied head
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 1024, "num_attention_heads": 8, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 2048, "vocab_size": 2048, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 256},
+    "max_position_embeddings": 1024, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+}
+SMALL_F = {  # head_dim 128, GQA 12:4, a width of three half-stages, a vocabulary that is no multiple of 16, untied
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 3, "hidden_size": 1536, "num_attention_heads": 12, "num_key_value_heads": 4,
+    "head_dim": 128, "intermediate_size": 3072, "vocab_size": 3000, "rope_theta": 250000.0,
+    "rope_scaling": {"rope_type": "linear", "factor": 4.0},
+    "max_position_embeddings": 1024, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": SMALL_E, "F": SMALL_F}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "F": 5}
+NORM_STD = {"A": 0.0, "B": 0.1, "C": 0.2, "D": 0.05, "E": 0.1, "F": 0.15}
+
+# The benchmark's shape itself (Llama 3.2 1B)
+LLAMA_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 16, "hidden_size": 2048,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192,
+    "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": True,
+}
 
 
 def tensor_shapes(cfg):
@@ -72,18 +101,20 @@ def bf16_round(a):
     return (to_bf16_bits(a).astype(np.uint32) << 16).view(np.float32)
 
 
-def random_weights(cfg, seed, norm_std=0.0, std=0.02, qk_gain=1.0):
+def random_weights(cfg, seed, norm_std=0.0, std=0.02, qk_gain=1.0, draw32=False):
     """float32 arrays whose values are exact in bfloat16, so that the 32-bit and the
     bfloat16 engine and the plain implementation all start from the same numbers.
     ``qk_gain`` scales the query and key projections: a gain of some tens makes the
-    softmax peaked, so that one wrong or missing key changes the logits."""
+    softmax peaked, so that one wrong or missing key changes the logits.  ``draw32`` draws in
+    float32 (another stream of numbers, several times faster: for models of a billion values)."""
     rng = np.random.default_rng(seed)
     w = {}
     for name, shape in tensor_shapes(cfg):
         if name.endswith("norm.weight") or name.endswith("layernorm.weight"):
             a = np.ones(shape, dtype=np.float32) + rng.standard_normal(shape).astype(np.float32) * norm_std
         else:
-            a = rng.standard_normal(shape).astype(np.float32) * std
+            a = (rng.standard_normal(shape, dtype=np.float32) if draw32
+                 else rng.standard_normal(shape).astype(np.float32)) * np.float32(std)
             if "q_proj" in name or "k_proj" in name:
                 a = a * qk_gain
         w[name] = bf16_round(a)

@@ -446,3 +446,77 @@ def test_scratch_views_are_kept_until_a_buffer_moves():
     rt.reserve_rows = 64
     wide = rt.buffer("z", (2, 5))
     assert rt.buffer("z", (64, 5)).data_ptr() == wide.data_ptr(), "made for reserve_rows rows at once"
+
+
+# ----------------------------------------------------------------------------- a kernel that gave up
+
+class _WordRunner:
+    """Stands in for ModelRunner: moves the cache on as a step does and, at a chosen step, sets
+    the word that a kernel sets when one of its bounded waits runs out."""
+
+    def __init__(self, cache, word):
+        self.cache, self.word = cache, word
+        self.steps, self.fault_at = 0, None
+
+    def step(self, entries, device_tokens=None):
+        self.cache.reserve([(e.seq, len(e.tokens)) for e in entries])
+        for e in entries:
+            self.cache.commit(e.seq, len(e.tokens))
+        self.steps += 1
+        if self.steps == self.fault_at:
+            self.word[0] = 2
+        return sum(len(e.want) for e in entries) or None
+
+
+class _WordSampler:
+    """Stands in for Sampler: the word travels with the tokens and ``collect`` raises, as the
+    real one does, when it is not zero."""
+
+    device_ids = None
+
+    def __init__(self, word):
+        self.word = word
+
+    def launch(self, n_rows, params, indices, histories=()):
+        return (self.word[0], n_rows)
+
+    def collect(self, handle):
+        from mlxforge_b200.csrc.binding import KernelError
+        if handle is None:
+            return []
+        code, n = handle
+        if code:
+            self.word[0] = 0
+            raise KernelError(f"a kernel's bounded wait ran out (code {code})")
+        return [7] * n
+
+
+@pytest.mark.parametrize("pipeline", [False, True])
+def test_a_kernel_that_gave_up_ends_every_request_with_error(pipeline):
+    """The engine's own loop around stand-ins for the step and the sampler: when the status word
+    comes back non-zero, no token of that step is emitted, every request ends with "error", all
+    pages and slots come back, and the engine serves the next request."""
+    from types import SimpleNamespace
+    from mlxforge_b200.csrc.binding import KernelError
+    from mlxforge_b200.engine.engine import Engine, EngineConfig
+    word = [0]
+    cache = manager(max_tokens=1024)
+    runner = _WordRunner(cache, word)
+    model = SimpleNamespace(spec=SimpleNamespace(vocab_size=100, eos_token_ids=()))
+    cfg = EngineConfig(model_spec="-", max_running=8, token_budget=64, prefill_chunk=16, pipeline=pipeline)
+    eng = Engine.from_parts(cfg, model, cache, runner, _WordSampler(word))
+    reqs = [eng.submit_ids(list(range(1, 1 + n)), GREEDY, max_tokens=40) for n in (5, 30, 12)]
+    runner.fault_at = 6
+    with pytest.raises(KernelError):
+        for _ in range(100):
+            eng.step()
+    assert runner.steps >= 6
+    assert all(r.finished and r.finish_reason == "error" and "bounded wait" in r.error for r in reqs)
+    assert eng.idle
+    cache.check()
+    assert cache.free_pages() == cache.total_pages() and cache.slots.n_free == 8
+    emitted = [len(r.output_ids) for r in reqs]
+    again = eng.submit_ids([1, 2, 3], GREEDY, max_tokens=4)
+    eng.run_until_idle()
+    assert again.finish_reason == "length" and again.output_ids == [7] * 4
+    assert [len(r.output_ids) for r in reqs] == emitted

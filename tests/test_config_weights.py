@@ -237,3 +237,99 @@ def test_command_line_without_a_gpu(tmp_path):
     if not torch.cuda.is_available():
         r = run("generate", str(tmp_path / "m"), "1,2,3", "4")
         assert r.returncode != 0 and "no CPU fallback" in r.stderr
+
+
+def _split_into_shards(tmp_path, cfg, weights, n_first):
+    """A folder with config.json, two shard files and model.safetensors.index.json, as the
+    reference reads it (src/core/weights.cpp:208-249; its own test: tests/core/weights_test.cpp:23-106)."""
+    names = list(weights)
+    first, second = {n: weights[n] for n in names[:n_first]}, {n: weights[n] for n in names[n_first:]}
+    d = str(tmp_path)
+    for fname, part in (("model-00001-of-00002.safetensors", first), ("model-00002-of-00002.safetensors", second)):
+        write_model_dir(os.path.join(d, "_part"), cfg, part)
+        os.replace(os.path.join(d, "_part", "model.safetensors"), os.path.join(d, fname))
+    index = {"metadata": {"total_size": 0},
+             "weight_map": {**{n: "model-00001-of-00002.safetensors" for n in first},
+                            **{n: "model-00002-of-00002.safetensors" for n in second}}}
+    with open(os.path.join(d, "model.safetensors.index.json"), "w") as f:
+        json.dump(index, f)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    return d
+
+
+def test_a_folder_of_two_shards_loads_like_one_file(tmp_path):
+    import torch
+    from mlxforge_b200.config import get_architecture
+    from mlxforge_b200.engine.runtime import Runtime
+    from mlxforge_b200.models.decoder import DecoderModel
+    from mlxforge_b200.weights import load_tensors
+    from mlxforge_b200.weights.safetensors_io import model_files
+    w = random_weights(TINY_B, seed=9, norm_std=0.1)
+    d = _split_into_shards(tmp_path / "sharded", TINY_B, w, n_first=11)
+    files = model_files(d)
+    assert [os.path.basename(f) for f in files] == ["model-00001-of-00002.safetensors",
+                                                    "model-00002-of-00002.safetensors"]
+    c = config_from_json(TINY_B)
+    model = DecoderModel(get_architecture(c.architecture).build_spec(c), Runtime(torch.float32, "cpu"))
+    got = load_tensors(d, model.tensor_specs(), "cpu", exact=True)
+    assert set(got) == set(w)
+    for name, a in w.items():
+        assert np.array_equal(got[name].float().numpy(), a), name
+    model.bind(got)        # every part finds its tensors, whichever file they came from
+
+    # a tensor that neither shard has and one that the model does not know: still ONE error for both
+    os.remove(os.path.join(d, "model-00002-of-00002.safetensors"))
+    second = {n: a for n, a in list(w.items())[11:] if n != "model.norm.weight"}
+    second["model.layers.0.self_attn.q_proj.bias"] = np.zeros(4, dtype=np.float32)
+    write_model_dir(os.path.join(d, "_part"), TINY_B, second)
+    os.replace(os.path.join(d, "_part", "model.safetensors"), os.path.join(d, "model-00002-of-00002.safetensors"))
+    with pytest.raises(WeightError) as ei:
+        load_tensors(d, model.tensor_specs(), "cpu")
+    assert ei.value.missing == ["model.norm.weight"]
+    assert ei.value.unexpected == ["model.layers.0.self_attn.q_proj.bias"]
+
+
+def test_an_index_with_a_missing_shard_falls_back_to_the_single_file_or_fails(tmp_path):
+    from mlxforge_b200.weights.safetensors_io import model_files
+    w = random_weights(TINY_A, seed=9)
+    d = _split_into_shards(tmp_path / "sharded", TINY_A, w, n_first=5)
+    os.remove(os.path.join(d, "model-00001-of-00002.safetensors"))
+    with pytest.raises(SafetensorsError, match=r"no model.safetensors\[.index.json\]"):
+        model_files(d)
+    write_model_dir(d, TINY_A, w)                      # a whole model.safetensors beside the broken index
+    assert [os.path.basename(f) for f in model_files(d)] == ["model.safetensors"]
+    with open(os.path.join(d, "model.safetensors.index.json"), "w") as f:
+        f.write('{"metadata": {}}')
+    with pytest.raises(SafetensorsError, match="has no 'weight_map' object"):
+        model_files(d)
+
+
+def test_rope_scaling_override_replaces_the_checkpoints_wholesale():
+    """``rope_scaling`` given to the engine or on the command line replaces the checkpoint's
+    object; nothing of the old one survives (src/core/config.cpp:282-300; the reference's test:
+    tests/model/rope_scaling_test.cpp:116-221).  The frequencies the position encoding is built
+    with are those of the plain implementation for a config that had the override to begin with."""
+    from mlxforge_b200.config.model_config import apply_rope_scaling_override
+    from mlxforge_b200.models.llama import build_llama_spec
+    from mlxforge_b200.parts.rope import rope_frequencies
+    assert TINY_B["rope_scaling"]["rope_type"] == "llama3"
+    j = apply_rope_scaling_override(TINY_B, '{"rope_type": "linear", "factor": 4.0}')
+    c = config_from_json(j)
+    rs = c.rope_scaling
+    assert (rs.rope_type, rs.factor, rs.low_freq_factor, rs.high_freq_factor,
+            rs.original_max_position_embeddings) == ("linear", 4.0, 1.0, 1.0, 0)
+    position = build_llama_spec(c).layers[0].mixer.params["position"]
+    got = rope_frequencies(position.params["rotary_dim"], position.params["theta"], position.params["scaling"])
+    want = P.rope_frequencies(dict(TINY_B, rope_scaling={"rope_type": "linear", "factor": 4.0}))
+    assert np.array_equal(got, want)
+    assert not np.array_equal(got, P.rope_frequencies(TINY_B))
+    # onto a checkpoint without scaling, and an override the engine cannot compute
+    c2 = config_from_json(apply_rope_scaling_override(TINY_A, json.dumps(TINY_B["rope_scaling"])))
+    assert c2.rope_scaling.rope_type == "llama3" and c2.rope_scaling.original_max_position_embeddings == 32
+    with pytest.raises(ConfigError, match="unsupported rope_scaling rope_type 'yarn'"):
+        config_from_json(apply_rope_scaling_override(TINY_A, '{"rope_type": "yarn", "factor": 2.0}'))
+    with pytest.raises(ConfigError, match="invalid rope_scaling override JSON"):
+        apply_rope_scaling_override(TINY_A, '{"rope_type": ')
+    with pytest.raises(ConfigError, match="must be a JSON object"):
+        apply_rope_scaling_override(TINY_A, '[4.0]')

@@ -294,3 +294,23 @@ def test_steps_launched_ahead_change_no_token(tiny, dtype):
         assert n0 == 0 and n1 >= 20, "the second run must have launched steps ahead"
         assert ahead == plain and ahead_eos == plain_eos
         assert plain_eos[0][1] == "stop" and len(plain_eos[0][0]) <= 9
+
+
+def test_rope_scaling_override_changes_what_is_generated(tiny):
+    """The engine's ``rope_scaling`` option replaces the checkpoint's object: the tokens are those
+    of the plain implementation for a config that has the override, in the engine and through the
+    command line's ``--rope-scaling``."""
+    d, cfg, w = tiny["B"]
+    override = {"rope_type": "linear", "factor": 4.0}
+    prompt = random_prompt(cfg, 70, 5)
+    import json
+    want = P.generate(dict(cfg, rope_scaling=override), w, prompt, 10)
+    plain = P.generate(cfg, w, prompt, 10)
+    assert want != plain, "the override must matter for this prompt, or the test shows nothing"
+    assert _engine(d, rope_scaling=json.dumps(override)).generate(prompt, max_tokens=10) == want
+    assert _engine(d).generate(prompt, max_tokens=10) == plain
+    r = subprocess.run([sys.executable, "-m", "mlxforge_b200", "generate", d, ",".join(map(str, prompt)), "10",
+                        "--dtype", "float32", "--rope-scaling", json.dumps(override)],
+                       capture_output=True, text=True, cwd=ROOT)
+    assert r.returncode == 0, r.stderr
+    assert [int(t) for t in r.stdout.strip().splitlines()[-1].replace(",", " ").split()] == want

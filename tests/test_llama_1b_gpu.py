@@ -1,0 +1,75 @@
+"""The benchmark's own shape — Llama 3.2 1B: 16 layers, width 2048, 32 query and 8 key/value heads
+of 64, intermediate size 8192, a vocabulary of 128256, llama3 rope scaling, tied head — with
+random weights, through trace replay in 32-bit and in bfloat16, against the plain implementation
+in float64: a prompt whole, its last tokens one by one, and steps that mix portions of some
+requests with decoded tokens of others.  The bfloat16 run must go through the kernels that the
+benchmark times."""
+import io
+
+import numpy as np
+import pytest
+
+import plain_llama as P
+import trace_tools as TT
+from helpers import LLAMA_1B, random_prompt, random_weights, write_model_dir
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-4
+BF16_NOISE_FACTOR = 3.0
+
+
+class UpcastOnRead(dict):
+    """The weights stay in float32 (their values are exact in bfloat16) and become float64 only
+    while a function of the plain implementation holds them: 1.2 billion float64 values at once
+    would be 10 GB."""
+
+    def __getitem__(self, name):
+        return dict.__getitem__(self, name).astype(np.float64)
+
+
+@pytest.fixture(scope="module")
+def llama_1b(tmp_path_factory):
+    cfg = LLAMA_1B
+    w = random_weights(cfg, seed=7, norm_std=0.1, qk_gain=4.0, draw32=True)
+    d = write_model_dir(str(tmp_path_factory.mktemp("llama_1b") / "model"), cfg, w, "bfloat16")
+    w64 = UpcastOnRead(w)
+    reqs = {"p0": random_prompt(cfg, 48, 70), "p1": random_prompt(cfg, 21, 71), "p2": random_prompt(cfg, 34, 72)}
+    expected = {rid: P.forward_logits(cfg, w64, toks) for rid, toks in reqs.items()}
+    P.ROUND = P.round_bf16
+    try:
+        noise = max(float(np.max(np.abs(P.forward_logits(cfg, w64, toks) - expected[rid])))
+                    for rid, toks in reqs.items())
+    finally:
+        P.ROUND = None
+    scale = max(float(np.max(np.abs(e))) for e in expected.values())
+    return d, cfg, reqs, expected, {"float32": TOL_F32 * max(1.0, scale), "bfloat16": BF16_NOISE_FACTOR * noise}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_llama_1b_logits_in_every_cutting(llama_1b, tmp_path, dtype):
+    from mlxforge_b200.csrc import binding
+    from mlxforge_b200.engine.replay import make_runner, replay
+    d, cfg, reqs, expected, tols = llama_1b
+    first = {"p0": reqs["p0"]}
+    traces = {"whole": TT.whole(first), "decode_tail": TT.decode_tail(first, tail=8),
+              "portions": TT.portions(first, sizes=(19, 2, 16, 5)), "mixed": TT.mixed(reqs, max_live=3, seed=1)}
+    runner = make_runner(d, dtype, max(t.live_tokens_rounded() for t in traces.values()))
+    for pool in runner.cache._k + runner.cache._v:
+        pool.fill_(1.0e30)
+    before = binding.kernel_launches()
+    for name, trace in traces.items():
+        out_dir = str(tmp_path / name)
+        replay(runner, trace.lines(), out_dir, done=io.StringIO())
+        runner.cache.check()
+        got = TT.read_outputs(trace, out_dir, cfg["vocab_size"])
+        assert got
+        d_max, where = TT.worst(got, expected)
+        assert d_max <= tols[dtype], (f"{name} {dtype}: max abs diff {d_max:.3e} at {where}, first beyond "
+                                      f"tolerance {tols[dtype]:.3e} at {TT.first_bad(got, expected, tols[dtype])}")
+    ran = {k: v - before[k] for k, v in binding.kernel_launches().items()}
+    if dtype == "float32":
+        assert ran["gemm_f32"] > 0 and ran["attn_generic"] > 0 and ran["stream_tmap"] == 0, ran
+    else:
+        # the decode steps: weights by one tensor copy per stage, attention by tensor copies
+        assert ran["stream_tmap"] > 0 and ran["attn_decode_tma"] + ran["attn_decode_tma_merged"] > 0, ran

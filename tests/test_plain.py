@@ -95,3 +95,35 @@ def test_engine_draw_is_the_plain_draw():
     for seed in (0, 1, 12345, 2**40 + 3):
         for i in range(50):
             assert uniform_draw(seed, i) == P.uniform_for(seed, i)
+
+
+def test_rms_norm_against_the_reference_fixture():
+    """``embeddings.npy -> attn_norm0.npy`` of the reference's fixtures (six positions of
+    Llama-3.2-1B, layer 0's first norm, float16; tests/golden/make_rmsnorm_golden.py).  The
+    norm's weight is not a fixture, but it is one vector for all positions: the weight that
+    position 0 implies has to reproduce positions 1..5.  The rows' mean squares differ by a
+    factor of two and are only thirty times eps, so a missing or misplaced eps, a sum in place
+    of the mean, a mean over the wrong axis or a centred norm all miss by several times the
+    float16 rounding that the right formula (src/model/decoder_model.cpp:206-208) stays within.
+    (A weight applied as ``1 + w`` cannot be told from ``w`` without the checkpoint.)"""
+    a = np.load(os.path.join(os.path.dirname(__file__), "golden", "rmsnorm_anchor.npz"))
+    x, y = a["x"].astype(np.float64), a["y"].astype(np.float64)
+    eps = 1e-5
+
+    def miss(unit_norm):
+        u = unit_norm(x)
+        ok = np.abs(u[0]) > 1e-3                      # channels where position 0 says something about the weight
+        w = y[0] / np.where(ok, u[0], 1.0)
+        return float(np.abs(u[1:] * w - y[1:])[:, ok].max())
+
+    ones = np.ones(x.shape[1])
+    assert miss(lambda v: P.rms_norm(v, ones, eps)) < 2.5e-3
+    wrong = {
+        "no eps": lambda v: v / np.sqrt((v * v).mean(-1, keepdims=True)),
+        "eps outside the root": lambda v: v / (np.sqrt((v * v).mean(-1, keepdims=True)) + eps),
+        "sum for mean": lambda v: v / np.sqrt((v * v).sum(-1, keepdims=True) + eps),
+        "over positions": lambda v: v / np.sqrt((v * v).mean(0, keepdims=True) + eps),
+        "centred": lambda v: (v - v.mean(-1, keepdims=True)) / np.sqrt(v.var(-1, keepdims=True) + eps),
+    }
+    for name, f in wrong.items():
+        assert miss(f) > 6e-3, name

@@ -85,10 +85,14 @@ def portions(requests, sizes=(7, 2, 5, 3, 2, 11, 4, 2, 16, 1, 9)):
     return t
 
 
-def mixed(requests, max_live=4, seed=0, decode_last=8, want_all=True):
-    """Up to ``max_live`` live requests: portions of some beside single decoded
-    tokens of others in the same step, a request now and then left out of a step,
-    new ones admitted as others end."""
+def total_tokens(requests):
+    return sum(len(t) for t in requests.values())
+
+
+def mixed(requests, max_live=4, seed=0, decode_last=8, want_all=True, max_portion=9):
+    """Up to ``max_live`` live requests: portions of some (2 to ``max_portion`` tokens) beside
+    single decoded tokens of others in the same step, a request now and then left out of a
+    step, new ones admitted as others end."""
     rng = np.random.default_rng(seed)
     t = Trace()
     waiting = list(requests.items())
@@ -103,7 +107,7 @@ def mixed(requests, max_live=4, seed=0, decode_last=8, want_all=True):
             if len(live) > 1 and rng.random() < 0.2:
                 continue                                   # sits this step out
             left = len(toks) - p
-            n = 1 if left <= decode_last else int(min(left - decode_last, rng.integers(2, 10)))
+            n = 1 if left <= decode_last else int(min(left - decode_last, rng.integers(2, max_portion + 1)))
             want = range(n) if want_all else ([n - 1] if p + n >= len(toks) - decode_last else [])
             entries.append((rid, p, toks[p:p + n], want))
             live[rid][1] = p + n
