@@ -24,6 +24,9 @@ class Runtime:
         self.dtype = dtype
         self.device = torch.device(device)
         self.precise = dtype == torch.float32
+        # the library's bfloat16 products must add their partial sums in 32-bit too (a split along K
+        # that reduces in bfloat16 would round more than once and depend on the number of rows)
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         self._buffers: Dict[str, torch.Tensor] = {}
         self._views: Dict[tuple, tuple] = {}
         # bumped whenever a scratch buffer moves: captured CUDA graphs hold the old addresses

@@ -290,6 +290,87 @@ def test_one_far_key_decides(kernel):
             assert np.max(np.abs(got[h] - pc.v[0][special, h // 4])) < 2e-2, (special, h)
 
 
+def _decisive_pools(pc, n, td):
+    """The pools of ``pc`` rebuilt from its (edited) key arrays; tails and unused pages stay NaN."""
+    kp = np.full(tuple(pc.k_pool.shape), np.nan, dtype=np.float32)
+    for b in range(pc.table.shape[1]):
+        m = min(pc.page, n - b * pc.page)
+        kp[pc.table[0, b], :, :m] = pc.k[0][b * pc.page:b * pc.page + m].transpose(1, 0, 2)
+    return dev(kp, td), pc.v_pool.to(td)
+
+
+DECISIVE_KERNELS = {
+    # name: (head size, prefill?, tcgen05 prefill, decode with tensor copies, merge inside)
+    "prefill tcgen05 64": (64, True, True, True, True),
+    "prefill tcgen05 128": (128, True, True, True, True),
+    "prefill mma.sync 64": (64, True, False, True, True),
+    "prefill mma.sync 48": (48, True, False, True, True),
+    "decode tensor copies": (64, False, True, True, True),
+    "decode tensor copies, merge kernel": (64, False, True, True, False),
+    "decode 64 without tensor copies": (64, False, True, False, True),
+    "decode 128": (128, False, True, True, True),
+}
+
+
+@pytest.mark.parametrize("window", [0, 600])
+@pytest.mark.parametrize("kernel", list(DECISIVE_KERNELS))
+def test_one_key_decides_at_every_edge(kernel, window):
+    """One key among 1400 matches the queries; everything else scores about zero.  Rows that may
+    see it must return its value, rows that may not must return the average of what they do
+    see.  The key is put at the window's first position of some row and just before it, at a
+    query's own position and just after it (the causal edge), at the first and last slot of a
+    page, on both sides of the borders of 64-key and 128-key tiles and of 128-query tiles, and
+    in another split of the keys than the query.  With random scores an edge that is off by one
+    key moves the output by a thousandth, far inside any tolerance; here it moves it by about 1."""
+    import torch
+    from mlxforge_b200.csrc import ops
+    hd, prefill, tc, tma, merge_inside = DECISIVE_KERNELS[kernel]
+    nh, nkv, n = 4, 2, 1400
+    q_len = 300 if prefill else 1
+    first = n - q_len                                   # position of the first query row
+    # key positions to try: relative to the rows' windows, to the causal edge, to pages and tiles
+    specials = {n - 1, n - 2, first, first + 1, first + 127, first + 128, first + 129, 1023, 1024, 1039, 1040, 511, 512}
+    if window:
+        specials |= {n - window, n - window - 1, first - window + 1, first - window, first - window + 128,
+                     n - window - 16, 800, 801}
+    else:
+        specials |= {0, 15, 16, 63, 64, 127, 128}
+    old_tma, old_merge = ops.set_decode_tma(tma), ops.set_decode_merge_inside(merge_inside)
+    ops.set_prefill_tcgen05(tc)
+    try:
+        for special in sorted(p for p in specials if 0 <= p < n):
+            pc = Paged([n], nkv, hd, dtype="float32", seed=special % 97)
+            pc.k[0][:] *= 0.05
+            pc.k[0][special] = 4.0                      # score 4 * hd / sqrt(hd) >= 27 against ~0 for the rest
+            k_pool, v_pool = _decisive_pools(pc, n, torch.bfloat16)
+            q = np.ones((q_len, nh, hd), dtype=np.float32)
+            out = torch.full((q_len, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+            qd = dev(q.reshape(q_len, -1), torch.bfloat16)
+            scale = hd ** -0.5
+            if prefill:
+                ops.attention_prefill(qd, k_pool, v_pool, out, dev(np.array([0], dtype=np.int32)),
+                                      dev(np.array([q_len], dtype=np.int32)), dev(np.array([n], dtype=np.int32)), 0,
+                                      q_len, pc.table_dev, pc.page, nh, nkv, hd, scale, window)
+            else:
+                n_o, n_ml = ops.attention_decode_scratch(1, nh, hd, n)
+                ops.attention_decode(qd, k_pool, v_pool, out, torch.empty(n_o, dtype=torch.float32, device="cuda"),
+                                     torch.empty(n_ml, dtype=torch.float32, device="cuda"),
+                                     dev(np.array([n - 1], dtype=np.int32)), dev(np.array([0], dtype=np.int32)),
+                                     pc.table_dev, pc.page, nh, nkv, hd, scale, window, n)
+            ops.check_kernel_status()
+            got = host(out).reshape(q_len, nh, hd)
+            for j in range(q_len):
+                pos = first + j
+                lo = max(0, pos - window + 1) if window else 0
+                want = pc.reference(q[j], 0, pos, scale, window)
+                d = np.max(np.abs(got[j] - want))
+                assert d < 2e-2, (kernel, window, special, "row", j, "pos", pos, "sees it" if lo <= special <= pos else "must not see it", d)
+    finally:
+        ops.set_decode_tma(old_tma)
+        ops.set_decode_merge_inside(old_merge)
+        ops.set_prefill_tcgen05(True)
+
+
 # ----------------------------------------------------------------------------- rope + cache write
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -27,11 +27,10 @@ LENGTHS = {"A": [5, 17, 31, 70, 100, 90, 120], "B": [1, 9, 40, 70, 131, 150], "C
 # rows (the tcgen05 gated product), start at odd offsets, and still go down to two tokens
 PORTIONS = {"E": (150, 2, 129, 7, 300, 128, 3, 131, 64, 200), "F": (131, 2, 260, 5, 128, 190, 3, 64)}
 MIXED_PORTION = {"E": 180, "F": 150}
-POISON = 1.0e30
-"""What the cache pools hold before a replay: a value that is finite (a masked slot of a page
-that is in use may be read and multiplied by a probability of zero) and so large that one key
-or value read from a slot that the trace never wrote throws the logits off by far more than any
-tolerance."""
+POISON = float("nan")
+"""What the cache pools hold before a replay: a key or a value that is used from a slot which
+the trace never wrote (a page that was handed out again, the tail of a last page, a page the
+block table does not name) makes the logits NaN."""
 
 
 def _requests(cfg, which):
