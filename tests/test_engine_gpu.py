@@ -296,11 +296,15 @@ def test_steps_launched_ahead_change_no_token(tiny, dtype):
         assert plain_eos[0][1] == "stop" and len(plain_eos[0][0]) <= 9
 
 
-def test_rope_scaling_override_changes_what_is_generated(tiny):
+def test_rope_scaling_override_changes_what_is_generated(tmp_path):
     """The engine's ``rope_scaling`` option replaces the checkpoint's object: the tokens are those
     of the plain implementation for a config that has the override, in the engine and through the
     command line's ``--rope-scaling``."""
-    d, cfg, w = tiny["B"]
+    from helpers import TINY_B, random_weights, write_model_dir
+    cfg = TINY_B
+    w = random_weights(cfg, seed=1, norm_std=0.1, std=0.1)       # large enough that the tokens vary
+    d = write_model_dir(str(tmp_path / "m"), cfg, w, "bfloat16")
+    w = {k: v.astype(np.float64) for k, v in w.items()}
     override = {"rope_type": "linear", "factor": 4.0}
     prompt = random_prompt(cfg, 70, 5)
     import json

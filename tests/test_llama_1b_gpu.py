@@ -31,7 +31,7 @@ class UpcastOnRead(dict):
 @pytest.fixture(scope="module")
 def llama_1b(tmp_path_factory):
     cfg = LLAMA_1B
-    w = random_weights(cfg, seed=7, norm_std=0.1, qk_gain=4.0, draw32=True)
+    w = random_weights(cfg, seed=7, norm_std=0.1, qk_gain=2.0, draw32=True)
     d = write_model_dir(str(tmp_path_factory.mktemp("llama_1b") / "model"), cfg, w, "bfloat16")
     w64 = UpcastOnRead(w)
     reqs = {"p0": random_prompt(cfg, 48, 70), "p1": random_prompt(cfg, 21, 71), "p2": random_prompt(cfg, 34, 72)}
