@@ -47,6 +47,11 @@ _SIGNATURES = {
     "mf_filter_logits": [_P, c_int, c_int, c_longlong, _P, _P, _P, _P, _P],
     "mf_kernel_kinds": [],
     "mf_reset_decode_tickets": [_P],
+    "mf_reset_mid_rows_tickets": [_P],
+    "mf_mid_rows_min": [],
+    "mf_set_mid_rows_chunks": [c_int],
+    "mf_mid_rows_max": [],
+    "mf_mid_rows_linear": [_P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P],
 }
 
 MF_ERRORS = {10001: "a size or option this kernel does not take", 10002: "an unsupported dtype"}
@@ -73,6 +78,8 @@ def library() -> ctypes.CDLL:
         lib.mf_kernel_name.restype = ctypes.c_char_p
         lib.mf_kernel_launches.argtypes = [c_int]
         lib.mf_kernel_launches.restype = c_longlong
+        lib.mf_mid_rows_scratch.argtypes = [c_int]
+        lib.mf_mid_rows_scratch.restype = c_longlong
         _LIB = lib
     return _LIB
 

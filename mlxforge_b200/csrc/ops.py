@@ -176,6 +176,7 @@ def kernel_gave_up(code: int, device=None) -> KernelError:
     have left half done (the decode-attention tickets), and returns the error to raise."""
     kernel_status(device).zero_()
     check(library().mf_reset_decode_tickets(_stream()), "reset_decode_tickets", launches=0)
+    check(library().mf_reset_mid_rows_tickets(_stream()), "reset_mid_rows_tickets", launches=0)
     return KernelError(f"a kernel's bounded wait ran out (code {code}: 1 = copy producer, 2 = consumer); "
                        "the results of the step are invalid")
 
@@ -214,6 +215,35 @@ def stream_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: b
     check(library().mf_stream_linear(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out), M, N, K,
                                      1 if swiglu else 0, kernel_status(x.device).data_ptr(), _stream()),
           "stream_linear")
+
+
+def mid_rows_range():
+    """(fewest, most) rows of x that ``mid_linear`` takes."""
+    return int(library().mf_mid_rows_min()), int(library().mf_mid_rows_max())
+
+
+def mid_rows_scratch(rows: int) -> int:
+    """float32 elements of scratch that ``mid_linear`` needs for ``rows`` rows of x."""
+    return int(library().mf_mid_rows_scratch(rows))
+
+
+def mid_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, swiglu: bool = False) -> None:
+    """out = x @ w^T for 17 to 128 rows of bfloat16 x on the tcgen05 tensor cores with the weights
+    streamed once (see gemm_mid_rows.cu); out bfloat16 or float32; with ``swiglu`` the rows of w
+    interleave gate and up in groups of 8 and out is [M, N/2] = silu(gate) * up.  ``scratch``:
+    float32, at least ``mid_rows_scratch(M)`` elements.  As with ``stream_linear``, ``w`` must not
+    be the output of the kernel launched just before."""
+    _need_cuda(x, w, out, scratch)
+    M, K = x.shape
+    N = w.shape[0]
+    want = (M, N // 2) if swiglu else (M, N)
+    if w.shape[1] != K or tuple(out.shape) != want:
+        raise KernelError(f"mid_linear: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if scratch.dtype != torch.float32 or scratch.numel() < mid_rows_scratch(M):
+        raise KernelError("mid_linear: scratch too small")
+    check(library().mf_mid_rows_linear(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out), scratch.data_ptr(),
+                                       M, N, K, 1 if swiglu else 0, kernel_status(x.device).data_ptr(), _stream()),
+          "mid_linear")
 
 
 def gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -38,6 +38,13 @@ class Runtime:
         self.skinny_enabled = True
         # rows at or below which the few-row product streams its weights by bulk copies
         self.stream_max_rows = 16
+        # 17 to 128 rows (a decode step of that many requests): the library's product by default, as
+        # in the reference above its own kernels' 32 rows; MLXFORGE_MID_ROWS=1 (or the "tcgen05"
+        # backend) takes this engine's own kernel with the weights on the M side of the tensor-core
+        # instruction instead (gemm_mid_rows.cu: correct at every size, and measured slower than
+        # the library on the 1B shape's matrices, so it is not the default)
+        self.mid_rows_enabled = os.environ.get("MLXFORGE_MID_ROWS", "0") == "1"
+        self.mid_max_rows = 128
         # many-row bfloat16 products: "library" (cuBLAS through torch.mm, as the reference uses
         # its library's matmul there), "tcgen05" (this engine's own tensor-memory kernel), or
         # "auto": the own kernel where it has SwiGLU in its epilogue (gate|up: one kernel instead
@@ -91,6 +98,9 @@ class Runtime:
         if self._skinny(x, w):
             (ops.stream_linear if x.shape[0] <= self.stream_max_rows else ops.skinny_linear)(x, w, out)
             return out
+        if self._mid(x, w):
+            ops.mid_linear(x, w, out, self.buffer("mid.partials", (ops.mid_rows_scratch(x.shape[0]),), torch.float32))
+            return out
         if self.gemm_backend == "tcgen05" and ops.gemm_ok(x, w):
             ops.gemm_bf16(x, w, out)
             return out
@@ -103,12 +113,20 @@ class Runtime:
     def _skinny(self, x, w) -> bool:
         return self.skinny_enabled and x.shape[0] <= self.skinny_max_rows and ops.skinny_ok(x, w)
 
+    def _mid(self, x, w) -> bool:
+        return ((self.mid_rows_enabled or self.gemm_backend == "tcgen05") and self.gemm_backend != "library"
+                and x.shape[0] <= self.mid_max_rows and ops.gemm_ok(x, w))
+
     def linear_swiglu(self, x: torch.Tensor, w_gu: torch.Tensor, group: int, out: torch.Tensor) -> torch.Tensor:
         """``out = silu(x Wg^T) * (x Wu^T)`` for a matrix whose rows interleave gate and
         up in groups of ``group``.  Few bfloat16 rows: one kernel with the product in
         its epilogue; otherwise the product, then the elementwise kernel."""
         if group == 8 and w_gu.shape[0] % 16 == 0 and self._skinny(x, w_gu):
             (ops.stream_linear if x.shape[0] <= self.stream_max_rows else ops.skinny_linear)(x, w_gu, out, swiglu=True)
+            return out
+        if group == 8 and w_gu.shape[0] % 16 == 0 and self._mid(x, w_gu):
+            ops.mid_linear(x, w_gu, out, self.buffer("mid.partials", (ops.mid_rows_scratch(x.shape[0]),), torch.float32),
+                           swiglu=True)
             return out
         own = self.gemm_backend == "tcgen05" or (self.gemm_backend == "auto"
                                                  and x.shape[0] >= self.fused_swiglu_min_rows)

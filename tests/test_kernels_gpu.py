@@ -418,6 +418,52 @@ def test_rope_kv_write(dtype, nh, nkv, hd, rot):
 
 # ----------------------------------------------------------------------------- few-row products
 
+@pytest.mark.parametrize("M", [17, 32, 33, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(304, 80), (2048, 2048), (3072, 2048), (1000, 136), (96, 200), (130, 64), (5000, 520),
+                                 (2048, 8192), (40000, 512), (300, 3080)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_mid_linear(M, N, K, out_dtype):
+    """The product for 17 to 128 rows: matrices of a few tiles that every block gets a piece of
+    (partial sums, tickets), of many tiles, tiles that end beyond N, K tails; run twice on the
+    same scratch, which starts full of NaN (the tickets must be back at zero, nothing stale read)."""
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(M * 7 + N)
+    x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    w = bf16_round((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32))
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    td = torch_dtype(out_dtype)
+    scratch = torch.full((ops.mid_rows_scratch(M),), float("nan"), dtype=torch.float32, device="cuda")
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    for _ in range(2):
+        out = torch.full((M, N), float("nan"), dtype=td, device="cuda")
+        ops.mid_linear(xd, wd, out, scratch)
+        ops.check_kernel_status()
+        got = host(out)
+        tol = 2e-5 * np.sqrt(K) if out_dtype == "float32" else 2.0 ** -7 * max(1.0, np.abs(want).max())
+        assert np.max(np.abs(got - want)) < tol, np.max(np.abs(got - want))
+
+
+@pytest.mark.parametrize("M,I,K", [(17, 136, 80), (64, 8192, 2048), (100, 64, 96), (128, 1000, 520)])
+def test_mid_linear_swiglu(M, I, K):
+    import torch
+    from mlxforge_b200.csrc import ops
+    rng = np.random.default_rng(M + I)
+    x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    wg = bf16_round((rng.standard_normal((I, K)) / np.sqrt(K)).astype(np.float32))
+    wu = bf16_round((rng.standard_normal((I, K)) / np.sqrt(K)).astype(np.float32))
+    gu = np.stack([wg.reshape(I // 8, 8, K), wu.reshape(I // 8, 8, K)], axis=1).reshape(2 * I, K)
+    g = x.astype(np.float64) @ wg.astype(np.float64).T
+    u = x.astype(np.float64) @ wu.astype(np.float64).T
+    want = g / (1.0 + np.exp(-g)) * u
+    scratch = torch.full((ops.mid_rows_scratch(M),), float("nan"), dtype=torch.float32, device="cuda")
+    for _ in range(2):
+        out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.mid_linear(dev(x, torch.bfloat16), dev(gu, torch.bfloat16), out, scratch, swiglu=True)
+        ops.check_kernel_status()
+        assert np.max(np.abs(host(out) - want)) < 2.0 ** -6 * max(1.0, np.abs(want).max())
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 304, 80), (8, 2048, 2048), (5, 307, 136), (16, 96, 200), (9, 1000, 64),
                                    (3, 128256, 64), (8, 16, 8192), (2, 5000, 520), (7, 40, 1032), (16, 4737, 1536),
                                    (3, 9000, 512), (11, 4744, 1024), (8, 300, 3072)])

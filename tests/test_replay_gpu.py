@@ -171,6 +171,22 @@ def test_replay_with_the_tcgen05_products(models, tmp_path, mode, monkeypatch):
         assert d_max <= tols["bfloat16"], (which, mode, d_max, where)
 
 
+def test_replay_with_the_mid_rows_product(models, tmp_path, monkeypatch):
+    """Steps of 17 to 128 tokens (portions of prompts beside decoded tokens) through this engine's
+    own product for that many rows instead of the library's."""
+    monkeypatch.setenv("MLXFORGE_MID_ROWS", "1")
+    from mlxforge_b200.csrc import ops
+    for which, mode in (("E", "mixed"), ("F", "portions"), ("C", "whole")):
+        d, cfg, reqs, expected, tols = models[(which, True)]
+        trace = MODES[mode](reqs, which)
+        out_dir, ran = _replay(d, "bfloat16", trace, tmp_path / which)
+        ops.check_kernel_status()
+        assert ran["mid_rows"] > 0, ran
+        got = TT.read_outputs(trace, out_dir, cfg["vocab_size"])
+        d_max, where = TT.worst(got, expected)
+        assert d_max <= tols["bfloat16"], (which, mode, d_max, where)
+
+
 @pytest.mark.parametrize("which,lengths", [("B", [300, 150, 40]), ("E", [700, 290, 40])])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_from_the_first_token(tmp_path, dtype, which, lengths):
