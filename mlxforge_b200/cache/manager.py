@@ -51,7 +51,7 @@ class CacheLayout:
     def bytes_per_request(self) -> int:
         total = 0
         for g in self.state:
-            n = 4
+            n = getattr(torch, getattr(g.need, "dtype", "float32")).itemsize
             for s in g.need.shape:
                 n *= s
             total += n * g.n_lanes
@@ -65,6 +65,17 @@ class KVLane:
 
     def __init__(self, k, v, group: int, need: PagedKV, page_size: int):
         self.k, self.v, self.group, self.need, self.page_size = k, v, group, need, page_size
+
+    def store(self, qkv, batch, q_out, n_heads: int, n_kv_heads: int, writes_cache: bool = True,
+              precise: bool = False) -> None:
+        """The lane's own write: from ``qkv`` ([T, (n_heads + 2 n_kv_heads) * head_dim], queries,
+        keys and values side by side, already position-encoded) the keys and values of token ``t``
+        go to page ``block_table[seq_of_token[t], p // page_size]``, slot ``p % page_size``
+        (``p = batch.positions[t]``) and the queries to ``q_out``.  Nothing is rotated here, so a
+        position encoding never has to know how the cache is laid out."""
+        from ..csrc import ops
+        ops.rope_kv_write(qkv, batch.positions, batch.seq_of_token, batch.block_table(self.group), self.page_size,
+                          None, q_out, self.k, self.v, n_heads, n_kv_heads, self.need.head_dim, 0, writes_cache, precise)
 
 
 class StateLane:
@@ -97,7 +108,8 @@ class CacheManager:
             shape = (g.n_lanes, self.n_pages, g.need.n_kv_heads, page_size, g.need.head_dim)
             self._k.append(torch.zeros(shape, dtype=dtype, device=device))
             self._v.append(torch.zeros(shape, dtype=dtype, device=device))
-        self._state = [torch.zeros((g.n_lanes, max_seqs) + tuple(g.need.shape), dtype=torch.float32, device=device)
+        self._state = [torch.zeros((g.n_lanes, max_seqs) + tuple(g.need.shape),
+                                   dtype=getattr(torch, getattr(g.need, "dtype", "float32")), device=device)
                        for g in layout.state]
 
     # ------------------------------------------------------------------ views for the model

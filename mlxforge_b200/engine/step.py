@@ -14,14 +14,13 @@ from __future__ import annotations
 
 import gc
 from collections import OrderedDict
-import weakref
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
-from ..cache.manager import CacheManager, KVLane
+from ..cache.manager import CacheManager
 from ..cache.pages import SequenceCache
 from ..csrc import ops
 
@@ -40,9 +39,10 @@ class StepBatch:
     """Device-side description of one step, as every part sees it.
 
     Tokens are laid out sequence after sequence; sequences that bring one token
-    (decoding) come first.  ``positions[t]`` is the token's index in its
-    sequence, ``seq_of_token[t]`` the row of its sequence in the block tables and
-    in ``slots``."""
+    (decoding) come first, and ``n_decode`` says how many there are: a fact about the
+    layout that a mixer may use (the attention mixer gives those rows to its decode
+    kernel) or ignore.  ``positions[t]`` is the token's index in its sequence,
+    ``seq_of_token[t]`` the row of its sequence in the block tables and in ``slots``."""
 
     def __init__(self):
         self.n_tokens = 0
@@ -64,15 +64,9 @@ class StepBatch:
         self.seq_ctx_len = None
         self._block_tables: Dict[int, torch.Tensor] = {}
         self.max_ctx = 0
-        self.runner = None
 
     def block_table(self, group: int) -> torch.Tensor:
         return self._block_tables[group]
-
-    def attention(self, q, lane: KVLane, out, n_heads: int, scale: float, window: int) -> None:
-        """Attention of this step's queries over ``lane``; the kernel is chosen by
-        dtype and by how many tokens each sequence brings."""
-        self.runner.attention(self, q, lane, out, n_heads, scale, window)
 
 
 class ModelRunner:
@@ -244,7 +238,6 @@ class ModelRunner:
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
         b = StepBatch()
-        b.runner = weakref.proxy(self)      # no cycle: the runner keeps the last batch (see _advance)
         b.n_seqs, b.n_tokens = R, T
         tokens = np.empty(T, dtype=np.int32)
         positions = np.empty(T, dtype=np.int32)
@@ -332,27 +325,3 @@ class ModelRunner:
             self._last = None
             self._pinned = torch.empty(cap, dtype=torch.int32, pin_memory=True)
             self._meta = torch.empty(cap, dtype=torch.int32, device=self.rt.device)
-
-    # ------------------------------------------------------------------ attention dispatch
-    def attention(self, batch: StepBatch, q, lane: KVLane, out, n_heads: int, scale: float, window: int) -> None:
-        """bfloat16: the sequences that bring one token (they come first in the
-        batch) go to the split-key decode kernel, the others to the prefill
-        kernel.  float32: the generic kernel for all."""
-        need = lane.need
-        table = batch.block_table(lane.group)
-        nd = batch.n_decode if q.dtype == torch.bfloat16 else 0
-        if nd > 0:
-            n_o, n_ml = ops.attention_decode_scratch(nd, n_heads, need.head_dim, batch.max_ctx)
-            ops.attention_decode(q[:nd], lane.k, lane.v, out[:nd],
-                                 self.rt.buffer("attn.part_o", (n_o,), torch.float32),
-                                 self.rt.buffer("attn.part_ml", (n_ml,), torch.float32),
-                                 batch.positions[:nd], batch.seq_of_token[:nd], table, lane.page_size, n_heads,
-                                 need.n_kv_heads, need.head_dim, scale, window, batch.max_ctx)
-        if nd < batch.n_tokens and q.dtype == torch.bfloat16:
-            ops.attention_prefill(q, lane.k, lane.v, out, batch.seq_q_start[nd:], batch.seq_q_len[nd:],
-                                  batch.seq_ctx_len[nd:], nd, max(batch.q_len[nd:]), table, lane.page_size,
-                                  n_heads, need.n_kv_heads, need.head_dim, scale, window)
-        elif nd < batch.n_tokens:
-            ops.attention_generic(q[nd:], lane.k, lane.v, out[nd:], batch.positions[nd:],
-                                  batch.seq_of_token[nd:], table, lane.page_size, n_heads, need.n_kv_heads,
-                                  need.head_dim, scale, window)

@@ -10,8 +10,8 @@ from typing import Dict, List, Optional
 import torch
 
 from ..cache.manager import CacheLayout, GroupLayout
-from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, FixedState, ModelSpec,
-                          PagedKV, TensorSpec, build_part)
+from ..parts.base import (EMBEDDINGS, HEADS, NORMS, FixedState, ModelSpec, PagedKV, TensorSpec, build_layer,
+                          build_part)
 from ..weights.loader import WeightError, load_tensors
 
 
@@ -20,13 +20,7 @@ class DecoderModel:
         self.spec = spec
         self.rt = runtime
         self.embedding = build_part(EMBEDDINGS, spec.embedding, runtime)
-        self.blocks = []
-        for ls in spec.layers:
-            block_cls = BLOCKS.get(ls.block)
-            self.blocks.append(block_cls(
-                build_part(MIXERS, ls.mixer, runtime), build_part(NORMS, ls.mixer_norm, runtime),
-                build_part(FEED_FORWARDS, ls.feed_forward, runtime),
-                build_part(NORMS, ls.feed_forward_norm, runtime), runtime))
+        self.blocks = [build_layer(ls, runtime) for ls in spec.layers]
         self.final_norm = build_part(NORMS, spec.final_norm, runtime)
         self.head = build_part(HEADS, spec.head, runtime)
         for i, item in enumerate(spec.schedule):
@@ -90,7 +84,7 @@ class DecoderModel:
         for i, item in enumerate(self.spec.schedule):
             if item.cache_of is not None:
                 src = item_lane[item.cache_of]
-                need = self.blocks[item.layer].mixer.cache_need()
+                need = self.blocks[item.layer].cache_need()
                 if src is None or src[0] != "paged":
                     raise ValueError(f"schedule item {i} reads the cache of item {item.cache_of}, which has none to share")
                 src_need = paged[src[1]][0]
@@ -98,7 +92,7 @@ class DecoderModel:
                     raise ValueError(f"schedule item {i} cannot read a cache of another geometry")
                 item_lane.append(src)
                 continue
-            need = self.blocks[item.layer].mixer.cache_need()
+            need = self.blocks[item.layer].cache_need()
             if need is None:
                 item_lane.append(None)
             elif isinstance(need, PagedKV):

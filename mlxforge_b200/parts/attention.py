@@ -19,8 +19,36 @@ from ..csrc import ops
 from .base import POSITIONS, Mixer, PagedKV, TensorSpec, build_part, register_mixer
 
 
+def paged_attention(rt, batch, q, lane, out, n_heads: int, scale: float, window: int) -> None:
+    """Attention of the step's queries over ``lane``; the kernel is chosen by dtype and by how
+    many tokens each sequence brings.  bfloat16: the sequences that bring one token (the batch
+    lays them out first: ``batch.n_decode``) go to the split-key decode kernel, the others to the
+    prefill kernel.  float32: the generic kernel for all."""
+    need = lane.need
+    table = batch.block_table(lane.group)
+    nd = batch.n_decode if q.dtype == torch.bfloat16 else 0
+    if nd > 0:
+        n_o, n_ml = ops.attention_decode_scratch(nd, n_heads, need.head_dim, batch.max_ctx)
+        ops.attention_decode(q[:nd], lane.k, lane.v, out[:nd],
+                             rt.buffer("attn.part_o", (n_o,), torch.float32),
+                             rt.buffer("attn.part_ml", (n_ml,), torch.float32),
+                             batch.positions[:nd], batch.seq_of_token[:nd], table, lane.page_size, n_heads,
+                             need.n_kv_heads, need.head_dim, scale, window, batch.max_ctx)
+    if nd < batch.n_tokens and q.dtype == torch.bfloat16:
+        ops.attention_prefill(q, lane.k, lane.v, out, batch.seq_q_start[nd:], batch.seq_q_len[nd:],
+                              batch.seq_ctx_len[nd:], nd, max(batch.q_len[nd:]), table, lane.page_size,
+                              n_heads, need.n_kv_heads, need.head_dim, scale, window)
+    elif nd < batch.n_tokens:
+        ops.attention_generic(q[nd:], lane.k, lane.v, out[nd:], batch.positions[nd:],
+                              batch.seq_of_token[nd:], table, lane.page_size, n_heads, need.n_kv_heads,
+                              need.head_dim, scale, window)
+
+
 @register_mixer("attention")
 class AttentionMixer(Mixer):
+    """``forward`` is four steps, each a method of its own, so that a variant (a norm on queries
+    and keys, a gate on the output, another kernel) overrides one step and keeps the rest."""
+
     graph_safe = True
 
     def __init__(self, params, prefix, runtime):
@@ -64,12 +92,26 @@ class AttentionMixer(Mixer):
     def cache_need(self):
         return PagedKV(self.n_kv, self.hd, self.window)
 
-    def forward(self, x, batch, cache, writes_cache: bool = True):
-        rt = self.rt
+    def project(self, x):
+        """[T, H] -> queries, keys and values side by side, [T, (n_heads + 2 n_kv) * head_dim]."""
         T = x.shape[0]
-        qkv = rt.linear(x, self.w_qkv, rt.buffer("attn.qkv", (T, (self.n_heads + 2 * self.n_kv) * self.hd)))
-        q = rt.buffer("attn.q", (T, self.n_heads * self.hd))
+        return self.rt.linear(x, self.w_qkv, self.rt.buffer("attn.qkv", (T, (self.n_heads + 2 * self.n_kv) * self.hd)))
+
+    def encode_and_store(self, qkv, batch, cache, writes_cache: bool):
+        """Position-encode queries and keys, append keys and values to the cache; returns the queries."""
+        q = self.rt.buffer("attn.q", (qkv.shape[0], self.n_heads * self.hd))
         self.position.rotate_and_store(qkv, batch, q, cache, self.n_heads, self.n_kv, writes_cache)
-        o = rt.buffer("attn.o", (T, self.n_heads * self.hd))
-        batch.attention(q, cache, o, self.n_heads, self.scale, self.window)
-        return rt.linear(o, self.w_o, rt.buffer("attn.delta", (T, self.hidden)))
+        return q
+
+    def attend(self, q, batch, cache):
+        o = self.rt.buffer("attn.o", (q.shape[0], self.n_heads * self.hd))
+        paged_attention(self.rt, batch, q, cache, o, self.n_heads, self.scale, self.window)
+        return o
+
+    def output(self, o):
+        return self.rt.linear(o, self.w_o, self.rt.buffer("attn.delta", (o.shape[0], self.hidden)))
+
+    def forward(self, x, batch, cache, writes_cache: bool = True):
+        qkv = self.project(x)
+        q = self.encode_and_store(qkv, batch, cache, writes_cache)
+        return self.output(self.attend(q, batch, cache))

@@ -1,8 +1,9 @@
 """What a model is made of, as data, and the interfaces its parts implement.
 
-A model is a ``ModelSpec``: an embedding, a list of ``LayerSpec`` (each naming a
-mixer, a feed-forward, their norms and the arrangement of the four in a block,
-every one by *kind* with its sizes and constants as parameters), a *schedule*
+A model is a ``ModelSpec``: an embedding, a list of ``LayerSpec`` (each naming its
+parts by role -- usually a mixer, a feed-forward and their norms, but a layer may
+leave one out or carry further ones -- and the arrangement that runs them, every
+one by *kind* with its sizes and constants as parameters), a *schedule*
 that says in which order layers run (a layer may appear twice; a run may read
 the cache another run wrote), a final norm and an output head.  The reference
 builds the same thing with virtual methods on one class (``attention /
@@ -37,13 +38,34 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: its four parts and how a block arranges them."""
+    """One layer: its parts by role and the arrangement (``block``) that runs them.
+
+    The four usual roles have fields of their own; any of them may be None (a layer
+    without a feed-forward, an arrangement with one norm).  ``extra`` holds further
+    parts as ``(role, family, spec)``, ``family`` being the registry the part is
+    built from: "mixer", "feed_forward" or "norm" (a norm after the mixer, a second
+    feed-forward, ...).  The arrangement finds all of them under their roles."""
 
     block: str                     # arrangement kind, e.g. "prenorm"
-    mixer: PartSpec
-    mixer_norm: PartSpec
-    feed_forward: PartSpec
-    feed_forward_norm: PartSpec
+    mixer: Optional[PartSpec] = None
+    mixer_norm: Optional[PartSpec] = None
+    feed_forward: Optional[PartSpec] = None
+    feed_forward_norm: Optional[PartSpec] = None
+    extra: Tuple[Tuple[str, str, PartSpec], ...] = ()
+
+    def part_specs(self) -> List[Tuple[str, str, PartSpec]]:
+        """Every part of the layer as (role, family, spec), in a fixed order."""
+        usual = (("mixer", "mixer", self.mixer), ("mixer_norm", "norm", self.mixer_norm),
+                 ("feed_forward", "feed_forward", self.feed_forward),
+                 ("feed_forward_norm", "norm", self.feed_forward_norm))
+        out = [(role, family, spec) for role, family, spec in usual if spec is not None]
+        seen = {role for role, _, _ in out}
+        for role, family, spec in self.extra:
+            if role in seen:
+                raise ValueError(f"layer names the role '{role}' twice")
+            seen.add(role)
+            out.append((role, family, spec))
+        return out
 
 
 @dataclass(frozen=True)
@@ -94,11 +116,13 @@ class PagedKV:
 
 @dataclass(frozen=True)
 class FixedState:
-    """Per-request state of fixed size, one tensor of ``shape`` (32-bit floats)
-    per run of the layer, zeroed when a request is admitted."""
+    """Per-request state of fixed size, one tensor of ``shape`` and ``dtype`` (a torch
+    dtype's name; 32-bit floats unless said otherwise) per run of the layer, zeroed
+    when a request is admitted."""
 
     shape: Tuple[int, ...]
     tag: str = ""
+    dtype: str = "float32"
 
 
 CacheNeed = Union[PagedKV, FixedState, None]
@@ -147,17 +171,28 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    """Turns integer positions into whatever the mixer applies to queries and keys."""
+    """Turns integer positions into whatever the mixer applies to queries and keys.
+
+    An encoding implements ``encode`` and knows nothing of pages: the cache lane stores
+    keys and values (``KVLane.store``).  One that has a kernel doing both at once (the
+    rotary encoding has) overrides ``rotate_and_store`` as well.  The mixer forwards this
+    part's ``tensor_specs`` and ``bind``, so an encoding may own tensors."""
+
+    def encode(self, q, k, batch) -> None:
+        """Apply the encoding in place.  ``q``: [T, n_heads, head_dim] and ``k``:
+        [T, n_kv_heads, head_dim] (views into the step's projections, compute dtype);
+        token ``t`` stands at ``batch.positions[t]`` of its sequence."""
+        raise NotImplementedError
 
     def rotate_and_store(self, qkv, batch, q_out, lane, n_heads, n_kv_heads, writes_cache: bool) -> None:
         """``qkv``: [T, (n_heads + 2 n_kv_heads) * head_dim], the step's projections side by
-        side.  Writes the encoded queries to ``q_out`` [T, n_heads * head_dim] and, if
-        ``writes_cache``, the encoded keys and the values of token ``t`` into page
-        ``batch.block_table(lane.group)[batch.seq_of_token[t], p // lane.page_size]``, slot
-        ``p % lane.page_size`` of ``lane.k`` / ``lane.v`` ([page, kv_head, slot, head_dim]),
-        with ``p = batch.positions[t]``.  The mixer forwards this part's ``tensor_specs`` and
-        ``bind``, so an encoding may own tensors."""
-        raise NotImplementedError
+        side.  Leaves the encoded queries in ``q_out`` [T, n_heads * head_dim] and, if
+        ``writes_cache``, the encoded keys and the values in the lane's pages.  The default
+        encodes in place and lets the lane store."""
+        T, hd = qkv.shape[0], lane.need.head_dim
+        nq, nk = n_heads * hd, n_kv_heads * hd
+        self.encode(qkv[:, :nq].view(T, n_heads, hd), qkv[:, nq:nq + nk].view(T, n_kv_heads, hd), batch)
+        lane.store(qkv, batch, q_out, n_heads, n_kv_heads, writes_cache, precise=self.rt.precise)
 
 
 class Mixer(Part):
@@ -181,16 +216,33 @@ class FeedForward(Part):
 class Block:
     """Arrangement of a layer's parts around the residual stream.  The stream
     travels as ``(residual, pending)``: ``pending`` is a delta not yet added, so
-    that the add can be fused with the next norm."""
+    that the add can be fused with the next norm.
 
-    def __init__(self, mixer: Mixer, mixer_norm: Norm, feed_forward: FeedForward,
-                 feed_forward_norm: Norm, runtime: "Any"):
-        self.mixer, self.mixer_norm = mixer, mixer_norm
-        self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
+    ``by_role`` holds the layer's parts under the roles its ``LayerSpec`` named; the
+    four usual ones are also attributes (None where the layer has none).  An
+    arrangement says with ``roles`` which parts it needs and fails at build time,
+    not in the middle of a step, when a layer does not bring them."""
+
+    roles: Tuple[str, ...] = ()
+
+    def __init__(self, by_role: Dict[str, Part], runtime: "Any"):
+        self.by_role = dict(by_role)
+        missing = [r for r in self.roles if r not in self.by_role]
+        if missing:
+            raise ValueError(f"{type(self).__name__} needs parts in the roles {missing}, the layer has "
+                             f"{sorted(self.by_role)}")
+        self.mixer = self.by_role.get("mixer")
+        self.mixer_norm = self.by_role.get("mixer_norm")
+        self.feed_forward = self.by_role.get("feed_forward")
+        self.feed_forward_norm = self.by_role.get("feed_forward_norm")
         self.rt = runtime
 
     def parts(self) -> List[Part]:
-        return [self.mixer, self.mixer_norm, self.feed_forward, self.feed_forward_norm]
+        return list(self.by_role.values())
+
+    def cache_need(self) -> CacheNeed:
+        """What this layer keeps per request: its mixer's need."""
+        return self.mixer.cache_need() if self.mixer is not None else None
 
     def forward(self, residual, pending, batch, cache, writes_cache: bool = True):
         raise NotImplementedError
@@ -241,3 +293,16 @@ register_head = HEADS.register
 
 def build_part(registry: _Registry, spec: PartSpec, runtime) -> Part:
     return registry.get(spec.kind)(spec.params, prefix=spec.prefix, runtime=runtime)
+
+
+FAMILIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS}
+
+
+def build_layer(spec: LayerSpec, runtime) -> Block:
+    """The layer's parts, each from its family's registry, in the arrangement it names."""
+    by_role = {}
+    for role, family, part in spec.part_specs():
+        if family not in FAMILIES:
+            raise KeyError(f"role '{role}': unknown family '{family}' (one of {sorted(FAMILIES)})")
+        by_role[role] = build_part(FAMILIES[family], part, runtime)
+    return BLOCKS.get(spec.block)(by_role, runtime)

@@ -12,6 +12,8 @@ from .base import Block, register_block
 
 @register_block("prenorm")
 class PreNormBlock(Block):
+    roles = ("mixer", "mixer_norm", "feed_forward", "feed_forward_norm")
+
     def forward(self, residual, pending, batch, cache, writes_cache: bool = True):
         x = self.mixer_norm.add_forward(residual, pending)
         d = self.mixer.forward(x, batch, cache, writes_cache)

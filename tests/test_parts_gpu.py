@@ -221,7 +221,9 @@ def test_block_part(dtype):
     ffn = build_part(FEED_FORWARDS, PartSpec("swiglu", {"hidden_size": H, "intermediate_size": INTER}, prefix="f."), h.rt)
     n1 = build_part(NORMS, PartSpec("rmsnorm", {"size": H, "eps": EPS}, prefix="n1."), h.rt)
     n2 = build_part(NORMS, PartSpec("rmsnorm", {"size": H, "eps": EPS}, prefix="n2."), h.rt)
-    block = BLOCKS.get("prenorm")(mixer, n1, ffn, n2, h.rt)
+    block = BLOCKS.get("prenorm")({"mixer": mixer, "mixer_norm": n1, "feed_forward": ffn, "feed_forward_norm": n2}, h.rt)
+    with pytest.raises(ValueError, match="needs parts in the roles"):
+        BLOCKS.get("prenorm")({"mixer": mixer, "mixer_norm": n1}, h.rt)
     w = {}
     for part in block.parts():
         for n, s in part.tensor_specs().items():

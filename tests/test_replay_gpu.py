@@ -165,7 +165,9 @@ def test_replay_with_the_tcgen05_products(models, tmp_path, mode, monkeypatch):
         trace = MODES[mode](reqs, which)
         out_dir, ran = _replay(d, "bfloat16", trace, tmp_path / which)
         ops.check_kernel_status()
-        assert ran["gemm_tc"] > 0 or (mode == "portions" and which != "E"), ran
+        # many-row products by the tcgen05 kernel, those of 17 to 128 rows by its few-row sibling
+        assert ran["gemm_tc"] + ran["mid_rows"] > 0 or (mode == "portions" and which != "E"), ran
+        assert which != "E" or mode == "mixed" or ran["gemm_tc"] > 0, ran
         got = TT.read_outputs(trace, out_dir, cfg["vocab_size"])
         d_max, where = TT.worst(got, expected)
         assert d_max <= tols["bfloat16"], (which, mode, d_max, where)

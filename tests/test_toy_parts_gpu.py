@@ -31,9 +31,9 @@ def _register():
     import torch
     from mlxforge_b200.config.model_config import ModelConfig
     from mlxforge_b200.config.registry import register_architecture
-    from mlxforge_b200.parts.base import (FeedForward, FixedState, LayerSpec, Mixer, ModelSpec, PartSpec,
-                                          PositionEncoding, ScheduleItem, TensorSpec, register_feed_forward,
-                                          register_mixer, register_position)
+    from mlxforge_b200.parts.base import (Block, FeedForward, FixedState, LayerSpec, Mixer, ModelSpec, PartSpec,
+                                          PositionEncoding, ScheduleItem, TensorSpec, register_block,
+                                          register_feed_forward, register_mixer, register_position)
 
     class DecayStateMixer(Mixer):
         """s_t = decay * s_{t-1} + x_t W_in^T ;  out_t = s_t W_out^T.  The state s lives in
@@ -42,6 +42,7 @@ def _register():
         def __init__(self, params, prefix, runtime):
             super().__init__(params, prefix, runtime)
             self.h, self.d, self.decay = params["hidden_size"], params["state_size"], params["decay"]
+            self.state_dtype = params.get("state_dtype", "float32")
 
         def tensor_specs(self):
             return {self.prefix + "in.weight": TensorSpec((self.d, self.h)),
@@ -52,16 +53,18 @@ def _register():
             self.w_out = tensors[self.prefix + "out.weight"].float()
 
         def cache_need(self):
-            return FixedState((self.d,), tag="decay")
+            return FixedState((self.d,), tag="decay", dtype=self.state_dtype)
 
         def forward(self, x, batch, cache, writes_cache=True):
-            u = x.float() @ self.w_in.t()
+            sd = cache.tensor.dtype                      # the state's own precision, as this mixer asked for it
+            u = (x.float() @ self.w_in.t()).to(sd)
+            w_out = self.w_out.to(sd)
             out = torch.empty((x.shape[0], self.h), dtype=torch.float32, device=x.device)
             for start, n, slot in zip(batch.q_start, batch.q_len, batch.slot_ids):
                 s = cache.tensor[slot].clone()
                 for t in range(start, start + n):
                     s = self.decay * s + u[t]
-                    out[t] = s @ self.w_out.t()
+                    out[t] = (s @ w_out.t()).float()
                 cache.tensor[slot] = s
             return out.to(x.dtype)
 
@@ -98,7 +101,8 @@ def _register():
 
     class LearnedPositions(PositionEncoding):
         """Learned vectors added to queries and keys: q += A[pos mod n], k += B[pos mod n], the same
-        for every head.  It owns two tensors and writes keys and values into the step's pages itself."""
+        for every head.  It owns two tensors and implements ``encode`` alone: storing keys and values
+        in pages is the cache lane's business."""
 
         def __init__(self, params, prefix, runtime):
             super().__init__(params, prefix, runtime)
@@ -112,17 +116,36 @@ def _register():
             self.a = tensors[self.prefix + "q.weight"].float()
             self.b = tensors[self.prefix + "k.weight"].float()
 
-        def rotate_and_store(self, qkv, batch, q_out, lane, n_heads, n_kv_heads, writes_cache):
-            T, hd = qkv.shape[0], self.hd
-            pos, seq = batch.positions.long(), batch.seq_of_token.long()
-            q, k, v = qkv.float().split([n_heads * hd, n_kv_heads * hd, n_kv_heads * hd], dim=1)
-            q_out.copy_((q.view(T, n_heads, hd) + self.a[pos % self.n][:, None]).reshape(T, -1).to(q_out.dtype))
-            if writes_cache:
-                page = batch.block_table(lane.group).long()[seq, pos // lane.page_size]
-                slot = pos % lane.page_size
-                lane.k[page, :, slot] = (k.view(T, n_kv_heads, hd) + self.b[pos % self.n][:, None]).to(lane.k.dtype)
-                lane.v[page, :, slot] = v.view(T, n_kv_heads, hd).to(lane.v.dtype)
+        def encode(self, q, k, batch):
+            pos = batch.positions.long()
+            q += self.a[pos % self.n][:, None].to(q.dtype)
+            k += self.b[pos % self.n][:, None].to(k.dtype)
 
+    class ParallelSandwich(Block):
+        """Another arrangement: the mixer and the feed-forward read the same normalised input, and
+        their sum goes through a norm of its own before it joins the stream:
+        ``h += out_norm( mixer(norm(h)) + feed_forward(norm(h)) )``.  One input norm, no
+        feed-forward norm, and a part in a role that the usual layer does not have."""
+
+        roles = ("mixer", "mixer_norm", "feed_forward", "out_norm")
+
+        def forward(self, residual, pending, batch, cache, writes_cache=True):
+            x = self.mixer_norm.add_forward(residual, pending)
+            total = self.mixer.forward(x, batch, cache, writes_cache).float() + self.feed_forward.forward(x, batch).float()
+            out = self.rt.buffer("toy.sandwich", tuple(total.shape))     # not the buffer the input norm writes
+            return residual, self.by_role["out_norm"].forward(total, out=out)
+
+    class MixerOnly(Block):
+        """A layer without a feed-forward: ``h += mixer(norm(h))``."""
+
+        roles = ("mixer", "mixer_norm")
+
+        def forward(self, residual, pending, batch, cache, writes_cache=True):
+            x = self.mixer_norm.add_forward(residual, pending)
+            return residual, self.mixer.forward(x, batch, cache, writes_cache)
+
+    register_block("toy_parallel_sandwich", ParallelSandwich, replace=True)
+    register_block("toy_mixer_only", MixerOnly, replace=True)
     register_position("toy_learned", LearnedPositions, replace=True)
     register_mixer("toy_decay_state", DecayStateMixer, replace=True)
     register_feed_forward("toy_top1_experts", Top1Experts, replace=True)
@@ -156,11 +179,19 @@ def _register():
             LayerSpec("prenorm", attn(2, nope, WINDOW), norm("layers.2.n1."), swiglu(2), norm("layers.2.n2.")),
             LayerSpec("prenorm", attn(3, rope, 0), norm("layers.3.n1."), swiglu(3), norm("layers.3.n2.")),
             LayerSpec("prenorm", attn(4, learned, 0), norm("layers.4.n1."), swiglu(4), norm("layers.4.n2.")),
+            # another arrangement, with a norm in a role of its own and no feed-forward norm
+            LayerSpec("toy_parallel_sandwich", mixer=attn(5, rope, 0), mixer_norm=norm("layers.5.n1."),
+                      feed_forward=swiglu(5), extra=(("out_norm", "norm", norm("layers.5.out_norm.")),)),
+            # a layer without a feed-forward, whose state is kept in float64
+            LayerSpec("toy_mixer_only",
+                      mixer=PartSpec("toy_decay_state", {"hidden_size": H, "state_size": D_STATE, "decay": DECAY,
+                                                         "state_dtype": "float64"}, prefix="layers.6.mix."),
+                      mixer_norm=norm("layers.6.n1.")),
         )
         # layer 0 runs twice (two caches of its own); the last run of layer 3 reads the cache
         # that the first run of layer 0 wrote and writes none
         schedule = (ScheduleItem(0), ScheduleItem(1), ScheduleItem(2), ScheduleItem(0), ScheduleItem(3, cache_of=0),
-                    ScheduleItem(4))
+                    ScheduleItem(4), ScheduleItem(5), ScheduleItem(6))
         return ModelSpec(hidden_size=H, vocab_size=V,
                          embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, prefix="embed."),
                          layers=layers, schedule=schedule, final_norm=norm("final_norm."),
@@ -177,9 +208,13 @@ def toy_weights(seed=3):
     for i in range(5):
         for n in ("n1", "n2"):
             w[f"layers.{i}.{n}.weight"] = bf16_round(1 + 0.1 * rng.standard_normal(H).astype(np.float32))
+    for n in ("layers.5.n1", "layers.5.out_norm", "layers.6.n1"):
+        w[f"{n}.weight"] = bf16_round(1 + 0.1 * rng.standard_normal(H).astype(np.float32))
+    w["layers.6.mix.in.weight"] = r(D_STATE, H)
+    w["layers.6.mix.out.weight"] = r(H, D_STATE)
     w["layers.4.pos.q.weight"] = r(N_POS, HD, std=0.5)
     w["layers.4.pos.k.weight"] = r(N_POS, HD, std=0.5)
-    for i in (0, 2, 3, 4):
+    for i in (0, 2, 3, 4, 5):
         w[f"layers.{i}.attn.q_proj.weight"] = r(NH * HD, H, std=0.3)
         w[f"layers.{i}.attn.k_proj.weight"] = r(NKV * HD, H, std=0.3)
         w[f"layers.{i}.attn.v_proj.weight"] = r(NKV * HD, H)
@@ -248,6 +283,21 @@ def plain_forward(w, tokens):
     h = attn_block(h, 0, 3, True, 0)
     h = attn_block(h, 3, 4, True, 0, kv_from=0)
     h = attn_block(h, 4, 5, "learned", 0)
+    # layer 5: attention and feed-forward side by side on one normalised input, their sum normalised
+    xn = P.rms_norm(h, w["layers.5.n1.weight"], EPS)
+    q, k, v = P.project_qkv(xn, w["layers.5.attn.q_proj.weight"], w["layers.5.attn.k_proj.weight"],
+                            w["layers.5.attn.v_proj.weight"], NH, NKV, HD)
+    q, k = P.apply_rope(q, pos, freqs), P.apply_rope(k, pos, freqs)
+    both = P.attention(q, k, v, HD ** -0.5, 0) @ w["layers.5.attn.o_proj.weight"].T + \
+        P.swiglu_mlp(xn, w["layers.5.mlp.gate_proj.weight"], w["layers.5.mlp.up_proj.weight"],
+                     w["layers.5.mlp.down_proj.weight"])
+    h = h + P.rms_norm(both, w["layers.5.out_norm.weight"], EPS)
+    # layer 6: the decaying state alone
+    u = P.rms_norm(h, w["layers.6.n1.weight"], EPS) @ w["layers.6.mix.in.weight"].T
+    s = np.zeros(D_STATE)
+    for t in range(T):
+        s = DECAY * s + u[t]
+        h[t] = h[t] + s @ w["layers.6.mix.out.weight"].T
     return P.rms_norm(h, w["final_norm.weight"], EPS) @ w["embed.weight"].T
 
 
@@ -263,9 +313,11 @@ def test_toy_architecture_is_registered_built_and_stepped(tmp_path):
     d = write_model_dir(str(tmp_path / "toy"), {"architectures": ["ToyForCausalLM"]}, w, "bfloat16")
     runner = make_runner(d, "float32", max_tokens=192)
     layout = runner.model.cache_layout
-    # two paged groups (full attention: three lanes; windowed: one) and one state group
-    assert sorted((g.need.window, g.n_lanes) for g in layout.paged) == [(0, 3), (WINDOW, 1)]
-    assert [(type(g.need), g.n_lanes) for g in layout.state] == [(FixedState, 1)]
+    # two paged groups (full attention: four lanes; windowed: one) and two state groups (the two
+    # decaying states differ in precision, so each has slots of its own)
+    assert sorted((g.need.window, g.n_lanes) for g in layout.paged) == [(0, 4), (WINDOW, 1)]
+    assert sorted((g.need.dtype, g.n_lanes) for g in layout.state) == [("float32", 1), ("float64", 1)]
+    assert {str(t.dtype) for t in runner.cache._state} == {"torch.float32", "torch.float64"}
     assert layout.item_lane[4] == layout.item_lane[0], "the last run reads the first run's lane"
 
     rng = np.random.default_rng(0)
