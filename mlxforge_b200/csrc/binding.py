@@ -35,8 +35,6 @@ _SIGNATURES = {
     "mf_stream_max_rows": [],
     "mf_set_stream_tensor_copies": [c_int],
     "mf_stream_linear": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P],
-    "mf_skinny_max_rows": [],
-    "mf_skinny_linear": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "mf_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int,
                              c_int, c_float, c_int, _P, _P],
     "mf_set_prefill_tcgen05": [c_int],

@@ -122,7 +122,6 @@ int mf_sm_count();
 enum MfKernel {
   MF_K_STREAM_ROWS = 0,       // few-row product, row-segment copies
   MF_K_STREAM_TMAP,           // few-row product, one tensor copy per stage
-  MF_K_SKINNY,                // few-row product without the copy engine (<= 32 rows)
   MF_K_MID_ROWS,              // product of 17..128 rows (tcgen05, weights on the M side)
   MF_K_GEMM_TC,               // many-row product, tcgen05
   MF_K_GEMM_TC_SWIGLU,        // the same with the gated epilogue

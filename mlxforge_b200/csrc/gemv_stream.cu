@@ -2,9 +2,9 @@
 // shared memory by the bulk-copy engine (TMA): the decode-time product of every
 // projection and of the vocabulary head.
 //
-// It computes what gemv_skinny.cu computes (same tensor-core tiling: weight rows are the
-// M side of mma.sync.m16n8k16, up to 8*NB rows of x the N side, bfloat16 in, float32
-// accumulation, the same two epilogues), and differs in how the weights arrive:
+// Weight rows are the M side of mma.sync.m16n8k16, up to 8*NB rows of x the N side, bfloat16
+// in, float32 accumulation; the epilogue stores the product or, for a W whose rows interleave
+// gate and up in groups of 8, silu(gate) * up.  How the weights arrive:
 //   * a block is persistent: it walks tiles of ROWS weight rows (tile, tile + grid, ...);
 //   * one producer thread issues cp.async.bulk copies of row segments (KT elements of each
 //     of the tile's rows) into a ring of STAGES shared-memory buffers and signals an
@@ -411,9 +411,15 @@ int dispatch(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, i
   if (n_sms <= 0) return MF_ERR_BAD_ARG;
   // few output rows: tiles of 8 rows, so that there are blocks for every SM
   const bool small = mode == 0 && (N + 15) / 16 < 2 * n_sms;
-  // Tensor copies only where every box lies inside the matrix along K (a whole number of
-  // stages): with K = 64, where boxes hang over the end of K, a stage was seen to be handed
-  // over before its rows had all arrived.  Rows past N are filled with zeros by the engine.
+  // Tensor copies only where no box hangs over the end of the matrix along K (K a whole number of
+  // stages).  A 3-D box some of whose outermost slices (spans of 64 columns) lie wholly outside
+  // the tensor is not accounted for as a box that lies inside is: with K = 64 (seven of a box's
+  // eight spans outside) and a barrier that is used again for the next such box, stages were
+  // handed over with another tile's rows in them (3 x 128256 x 64 fails on its first call after a
+  // device-wide wait, so it is no ordering fault of the caller; the same shapes pass where every
+  // block has so few tiles that no barrier is used twice).  Boxes that hang over along the ROWS
+  // (tiles beyond N here, rows of x beyond M in gemm_mid_rows.cu) are used again and again on one
+  // barrier without fault.  Such widths take the row-segment copies.
   if (K % (small ? 1024 : 512) == 0 && g_stream_tensor_copies) {
     // few tiles of many stages each: the blocks do not fill the device, so each keeps six stages on
     // their way instead of four
@@ -452,8 +458,10 @@ MF_API int mf_set_stream_tensor_copies(int on) {
   return 0;
 }
 
-// Arguments as mf_skinny_linear, plus `status`: a device int (may be null) that receives a
-// non-zero code if a wait inside the kernel ran out (1: producer, 2: consumer).
+// mode 0: out [M, N] in out_dtype.  mode 1: W rows interleave gate and up in groups of 8 (N a
+// multiple of 16) and out is [M, N / 2] = silu(gate) * up.  K must be a multiple of 8 and x, W
+// 16-byte aligned.  `status`: a device int (may be null) that receives a non-zero code if a wait
+// inside the kernel ran out (1: producer, 2: consumer).
 MF_API int mf_stream_linear(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K, int mode,
                             int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;

@@ -6,7 +6,7 @@ unsigned long long g_mf_kernel_launches[MF_K_COUNT] = {};
 
 namespace {
 const char* const kNames[MF_K_COUNT] = {
-    "stream_rows",      "stream_tmap",      "skinny",      "mid_rows",         "gemm_tc",
+    "stream_rows",      "stream_tmap",      "mid_rows",         "gemm_tc",
     "gemm_tc_swiglu",   "gemm_f32",         "attn_generic", "attn_prefill_mma", "attn_prefill_tc",
     "attn_decode",      "attn_decode_tma",  "attn_decode_tma_merged", "attn_decode_merge",
 };

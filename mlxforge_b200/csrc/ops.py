@@ -131,28 +131,10 @@ def set_prefill_tcgen05(on: bool) -> None:
     check(library().mf_set_prefill_tcgen05(1 if on else 0), "set_prefill_tcgen05", launches=0)
 
 
-def skinny_max_rows() -> int:
-    return int(library().mf_skinny_max_rows())
-
-
-def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the few-row product kernel takes these operands."""
+def few_rows_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the few-row product kernels take these operands (rows are read in 16-byte pieces)."""
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
-
-
-def skinny_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
-    """out = x @ w^T for at most ``skinny_max_rows()`` rows of bfloat16 x (out bfloat16
-    or float32); with ``swiglu`` the rows of w interleave gate and up in groups of 8
-    and out [M, N/2] is silu(gate) * up."""
-    _need_cuda(x, w, out)
-    M, K = x.shape
-    N = w.shape[0]
-    want = (M, N // 2) if swiglu else (M, N)
-    if w.shape[1] != K or tuple(out.shape) != want:
-        raise KernelError(f"skinny_linear: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
-    check(library().mf_skinny_linear(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out), M, N, K,
-                                     1 if swiglu else 0, _stream()), "skinny_linear")
 
 
 _STATUS = {}
@@ -201,8 +183,9 @@ def set_stream_tensor_copies(on: bool) -> None:
 
 
 def stream_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
-    """The few-row product with weights streamed by bulk copies (see gemv_stream.cu);
-    same operands and results as ``skinny_linear``, at most ``stream_max_rows()`` rows.
+    """out = x @ w^T for at most ``stream_max_rows()`` rows of bfloat16 x (out bfloat16 or
+    float32), the weights streamed by bulk copies (see gemv_stream.cu); with ``swiglu`` the rows
+    of w interleave gate and up in groups of 8 and out [M, N/2] is silu(gate) * up.
     The kernel starts fetching ``w`` before it waits for the kernel launched before it, so
     ``w`` must not be the output of that kernel (the engine's weights are written once, at
     load time)."""

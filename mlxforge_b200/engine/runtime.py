@@ -33,11 +33,10 @@ class Runtime:
         self.generation = 0
         # rows every per-token buffer is first made for, so that later, larger steps do not move it
         self.reserve_rows = 0
-        # rows at or below which the bfloat16 product runs the skinny kernel
-        self.skinny_max_rows = 16
+        # rows at or below which the bfloat16 product runs the few-row kernel that streams its weights
+        # by bulk copies (``skinny_mm`` off sends them to the library, as the reference's option does)
         self.skinny_enabled = True
-        # rows at or below which the few-row product streams its weights by bulk copies
-        self.stream_max_rows = 16
+        self.stream_max_rows = ops.stream_max_rows() if self.device.type == "cuda" else 16
         # 17 to 128 rows (a decode step of that many requests): the library's product by default, as
         # in the reference above its own kernels' 32 rows; MLXFORGE_MID_ROWS=1 (or the "tcgen05"
         # backend) takes this engine's own kernel with the weights on the M side of the tensor-core
@@ -87,16 +86,17 @@ class Runtime:
     # ------------------------------------------------------------------ products
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """``out = x @ w^T`` with ``w`` [out_features, in_features].  float32
-        operands use this engine's IEEE kernel; bfloat16 operands use the skinny
-        kernel for few rows and the library product otherwise, accumulating in
-        32-bit and rounding once to ``out``'s dtype."""
+        operands use this engine's IEEE kernel; bfloat16 operands use the streamed
+        few-row kernel up to 16 rows and the library product (or this engine's own
+        tcgen05 kernels, see ``gemm_backend``) above, accumulating in 32-bit and
+        rounding once to ``out``'s dtype."""
         if x.dtype == torch.float32 and w.dtype == torch.float32:
             ops.gemm_f32(x, w, out)
             return out
         if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             raise ops.KernelError(f"linear: operand dtypes {x.dtype} x {w.dtype} are not a supported pair")
         if self._skinny(x, w):
-            (ops.stream_linear if x.shape[0] <= self.stream_max_rows else ops.skinny_linear)(x, w, out)
+            ops.stream_linear(x, w, out)
             return out
         if self._mid(x, w):
             ops.mid_linear(x, w, out, self.buffer("mid.partials", (ops.mid_rows_scratch(x.shape[0]),), torch.float32))
@@ -111,7 +111,7 @@ class Runtime:
         return out
 
     def _skinny(self, x, w) -> bool:
-        return self.skinny_enabled and x.shape[0] <= self.skinny_max_rows and ops.skinny_ok(x, w)
+        return self.skinny_enabled and x.shape[0] <= self.stream_max_rows and ops.few_rows_ok(x, w)
 
     def _mid(self, x, w) -> bool:
         return ((self.mid_rows_enabled or self.gemm_backend == "tcgen05") and self.gemm_backend != "library"
@@ -122,7 +122,7 @@ class Runtime:
         up in groups of ``group``.  Few bfloat16 rows: one kernel with the product in
         its epilogue; otherwise the product, then the elementwise kernel."""
         if group == 8 and w_gu.shape[0] % 16 == 0 and self._skinny(x, w_gu):
-            (ops.stream_linear if x.shape[0] <= self.stream_max_rows else ops.skinny_linear)(x, w_gu, out, swiglu=True)
+            ops.stream_linear(x, w_gu, out, swiglu=True)
             return out
         if group == 8 and w_gu.shape[0] % 16 == 0 and self._mid(x, w_gu):
             ops.mid_linear(x, w_gu, out, self.buffer("mid.partials", (ops.mid_rows_scratch(x.shape[0]),), torch.float32),

@@ -435,6 +435,7 @@ def test_mid_linear(M, N, K, out_dtype):
     td = torch_dtype(out_dtype)
     scratch = torch.full((ops.mid_rows_scratch(M),), float("nan"), dtype=torch.float32, device="cuda")
     xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    torch.cuda.synchronize()      # the kernel fetches W before it waits for the kernel before it: W must be there
     for _ in range(2):
         out = torch.full((M, N), float("nan"), dtype=td, device="cuda")
         ops.mid_linear(xd, wd, out, scratch)
@@ -457,16 +458,19 @@ def test_mid_linear_swiglu(M, I, K):
     u = x.astype(np.float64) @ wu.astype(np.float64).T
     want = g / (1.0 + np.exp(-g)) * u
     scratch = torch.full((ops.mid_rows_scratch(M),), float("nan"), dtype=torch.float32, device="cuda")
+    xd, gud = dev(x, torch.bfloat16), dev(gu, torch.bfloat16)
+    torch.cuda.synchronize()      # the kernel fetches W before it waits for the kernel before it: W must be there
     for _ in range(2):
         out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device="cuda")
-        ops.mid_linear(dev(x, torch.bfloat16), dev(gu, torch.bfloat16), out, scratch, swiglu=True)
+        ops.mid_linear(xd, gud, out, scratch, swiglu=True)
         ops.check_kernel_status()
         assert np.max(np.abs(host(out) - want)) < 2.0 ** -6 * max(1.0, np.abs(want).max())
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 304, 80), (8, 2048, 2048), (5, 307, 136), (16, 96, 200), (9, 1000, 64),
                                    (3, 128256, 64), (8, 16, 8192), (2, 5000, 520), (7, 40, 1032), (16, 4737, 1536),
-                                   (3, 9000, 512), (11, 4744, 1024), (8, 300, 3072)])
+                                   (3, 9000, 512), (11, 4744, 1024), (8, 300, 3072), (13, 2050, 192), (8, 3000, 576),
+                                   (16, 700, 1088), (4, 5000, 320)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
 @pytest.mark.parametrize("tensor_copies", [True, False])
 def test_stream_linear(M, N, K, out_dtype, tensor_copies):
@@ -495,8 +499,12 @@ def _check_stream_linear(M, N, K, out_dtype):
     tol = 3e-6 * np.sqrt(K) * 4 if out_dtype == "float32" else 2.0 ** -8 * np.abs(want).max() + 1e-3
     assert np.max(np.abs(host(out) - want)) < tol
     if M > 1:
+        # a row's result does not depend on how many rows there are.  (The same W on the device: a
+        # W converted by the kernel launched just before would be read before that kernel is done.)
         out1 = torch.empty((1, N), dtype=torch_dtype(out_dtype), device="cuda")
-        ops.stream_linear(dev(x[M - 1:M], torch.bfloat16), dev(w, torch.bfloat16), out1)
+        x1 = dev(x[M - 1:M], torch.bfloat16)
+        torch.cuda.synchronize()
+        ops.stream_linear(x1, wd, out1)
         assert torch.equal(out1[0], out[M - 1])
     # the swiglu epilogue, when the shape allows it
     if N % 16 == 0 and out_dtype == "bfloat16":
@@ -514,65 +522,23 @@ def _check_stream_linear(M, N, K, out_dtype):
     ops.check_kernel_status()
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 304, 80), (8, 2048, 2048), (5, 307, 136), (16, 96, 200), (9, 1000, 64),
-                                   (32, 48, 72), (3, 128256, 64), (8, 16, 8192)])
-@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
-def test_skinny_linear(M, N, K, out_dtype):
-    import torch
-    from mlxforge_b200.csrc import ops
-    rng = np.random.default_rng(M * 1000 + N)
-    x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
-    w = bf16_round(rng.standard_normal((N, K)).astype(np.float32))
-    out = torch.full((M, N), float("nan"), dtype=torch_dtype(out_dtype), device="cuda")
-    ops.skinny_linear(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out)
-    want = x.astype(np.float64) @ w.astype(np.float64).T
-    # float32 accumulation of exact bfloat16 products; then one rounding to the output type
-    tol = 3e-6 * np.sqrt(K) * 4 if out_dtype == "float32" else 2.0 ** -8 * np.abs(want).max() + 1e-3
-    assert np.max(np.abs(host(out) - want)) < tol
-    # a row's result does not depend on the other rows
-    if M > 1:
-        out1 = torch.empty((1, N), dtype=torch_dtype(out_dtype), device="cuda")
-        ops.skinny_linear(dev(x[M - 1:M], torch.bfloat16), dev(w, torch.bfloat16), out1)
-        assert torch.equal(out1[0], out[M - 1])
-
-
-@pytest.mark.parametrize("M,I,K", [(1, 136, 80), (8, 8192, 2048), (13, 64, 96)])
-def test_skinny_swiglu(M, I, K):
-    import torch
-    from mlxforge_b200.csrc import ops
-    rng = np.random.default_rng(I)
-    x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
-    wg = bf16_round(rng.standard_normal((I, K)).astype(np.float32) * 0.2)
-    wu = bf16_round(rng.standard_normal((I, K)).astype(np.float32) * 0.2)
-    gu = np.stack([wg.reshape(I // 8, 8, K), wu.reshape(I // 8, 8, K)], axis=1).reshape(2 * I, K)
-    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device="cuda")
-    ops.skinny_linear(dev(x, torch.bfloat16), dev(gu, torch.bfloat16), out, swiglu=True)
-    g = x.astype(np.float64) @ wg.astype(np.float64).T
-    u = x.astype(np.float64) @ wu.astype(np.float64).T
-    silu = g / (1 + np.exp(-g))
-    want = silu * u
-    # float32 accumulation errors of the two sums (each at most 2^-19 of sum(|x||w|): K
-    # additions that may each lose 2^-23 of the running magnitude), carried through
-    # silu(g) * u (|silu'| <= 1.1), plus one bfloat16 rounding of the result
-    eg = 2.0 ** -19 * (np.abs(x).astype(np.float64) @ np.abs(wg).astype(np.float64).T)
-    eu = 2.0 ** -19 * (np.abs(x).astype(np.float64) @ np.abs(wu).astype(np.float64).T)
-    bound = 1.1 * eg * (np.abs(u) + eu) + np.abs(silu) * eu + 2.0 ** -8 * np.abs(want) + 1e-6
-    assert np.all(np.abs(host(out) - want) <= bound)
-
-
-def test_skinny_refuses_what_it_cannot_do():
+def test_few_row_products_refuse_what_they_cannot_do():
     import torch
     from mlxforge_b200.csrc import ops
     from mlxforge_b200.csrc.binding import KernelError
-    x = torch.zeros((2, 12), dtype=torch.bfloat16, device="cuda")      # K not a multiple of 8
+    x = torch.zeros((2, 12), dtype=torch.bfloat16, device="cuda")          # K no multiple of 8
     w = torch.zeros((16, 12), dtype=torch.bfloat16, device="cuda")
-    assert not ops.skinny_ok(x, w)
     with pytest.raises(KernelError, match="refused"):
-        ops.skinny_linear(x, w, torch.zeros((2, 16), dtype=torch.bfloat16, device="cuda"))
-    x = torch.zeros((40, 16), dtype=torch.bfloat16, device="cuda")     # too many rows
+        ops.stream_linear(x, w, torch.zeros((2, 16), dtype=torch.bfloat16, device="cuda"))
+    x = torch.zeros((17, 16), dtype=torch.bfloat16, device="cuda")         # more rows than the streamed product takes
     with pytest.raises(KernelError, match="refused"):
-        ops.skinny_linear(x, torch.zeros((16, 16), dtype=torch.bfloat16, device="cuda"),
-                          torch.zeros((40, 16), dtype=torch.bfloat16, device="cuda"))
+        ops.stream_linear(x, torch.zeros((16, 16), dtype=torch.bfloat16, device="cuda"),
+                          torch.zeros((17, 16), dtype=torch.bfloat16, device="cuda"))
+    x = torch.zeros((129, 16), dtype=torch.bfloat16, device="cuda")        # and than the 17-to-128-row product takes
+    with pytest.raises(KernelError, match="refused"):
+        ops.mid_linear(x, torch.zeros((16, 16), dtype=torch.bfloat16, device="cuda"),
+                       torch.zeros((129, 16), dtype=torch.bfloat16, device="cuda"),
+                       torch.zeros(ops.mid_rows_scratch(129), dtype=torch.float32, device="cuda"))
 
 
 # ----------------------------------------------------------------------------- prefill attention
@@ -661,7 +627,10 @@ def test_attention_prefill_tcgen05(nh, nkv, lengths, q_lens, window, hd):
 # ----------------------------------------------------------------------------- tcgen05 product
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (2048, 3072, 2048), (300, 520, 136), (17, 96, 80),
-                                   (129, 257, 72), (1000, 128, 4096), (64, 16384, 512)])
+                                   (129, 257, 72), (1000, 128, 4096), (64, 16384, 512),
+                                   # tiles that hang over M, N and K in the middle of a block's run of
+                                   # tiles: every barrier is used again after such a box
+                                   (300, 30000, 72), (200, 20000, 200)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
 def test_gemm_tcgen05(M, N, K, out_dtype):
     import torch

@@ -109,7 +109,7 @@ MODES = {
     "mixed_tight": _mixed_tight,
 }
 
-BF16_ONLY = ("stream_rows", "stream_tmap", "skinny", "mid_rows", "gemm_tc", "gemm_tc_swiglu", "attn_prefill_mma",
+BF16_ONLY = ("stream_rows", "stream_tmap", "mid_rows", "gemm_tc", "gemm_tc_swiglu", "attn_prefill_mma",
              "attn_prefill_tc", "attn_decode", "attn_decode_tma", "attn_decode_tma_merged", "attn_decode_merge")
 # Kernels that a replay of the two serving-shaped models must have gone through (any one of a
 # tuple), by mode: a replay that falls back to another kernel fails even if its logits are right.
