@@ -410,7 +410,7 @@ MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_pool,
                       *vv = (const __nv_bfloat16*)v_pool;
   __nv_bfloat16* oo = (__nv_bfloat16*)out;
-  if (hd == 64 && g_decode_tma) {
+  if ((hd == 64 || hd == 128) && g_decode_tma) {
     // the map's row count only bounds the unit's own range check; rows beyond the pool are never asked for
     int split = SPLIT_KEYS, merged = 0;
     const int rc = launch_decode_tma(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, 1ll << 28, positions,
@@ -425,7 +425,7 @@ MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_
       mf_count(MF_K_ATTN_DECODE_MERGE);
       const int max_splits = (max_ctx + split - 1) / split;
       dim3 mgrid(n_tokens, n_heads);
-      return (int)launch_dep(attn_decode_merge_kernel, mgrid, dim3(64), 0, stream, (const float*)part_o,
+      return (int)launch_dep(attn_decode_merge_kernel, mgrid, dim3(hd), 0, stream, (const float*)part_o,
                              (const float*)part_ml, oo, positions, n_heads, hd, window, max_splits, split);
     }
     if (rc != MF_ERR_BAD_ARG) return rc;

@@ -1,21 +1,23 @@
-// Decode attention for head size 64 with the keys and values brought in by the TMA unit.
+// Decode attention for head sizes 64 and 128 with the keys and values brought in by the TMA unit.
 //
 // It computes exactly what attn_decode_kernel (attention_decode.cu) computes and writes the
 // same per-split partial results, but is built around the memory system instead of around the
 // warps, and it merges its splits itself: the block that finishes the last split of a (token,
 // head group) adds the splits' results in their order and writes the output (see g_tickets).
 // Launches with more groups than there are tickets leave the merge to attn_decode_merge_kernel.
-//   * two persistent blocks per SM walk work items (token, KV head x head group, split of 512
-//     keys), item = block, block + grid, ...;
-//   * a producer warp issues one 2-D tensor copy per granule of 16 keys (a page holds whole
-//     granules, so a granule is 16 contiguous rows of the pool): 8 key boxes and 8 value boxes
-//     per stage of 128 keys, 128-byte swizzled, into a ring of STAGES stages, each signalled by
-//     an mbarrier; it runs ahead across item boundaries, so the two rings of an SM keep about
+//   * persistent blocks (two per SM for head size 64, one for 128: a stage of 128 keys and values
+//     is 32 or 64 KB) walk work items (token, KV head x head group, split of 512 keys or more),
+//     item = block, block + grid, ...;
+//   * a producer warp issues 2-D tensor copies per granule of 16 keys (a page holds whole
+//     granules, so a granule is 16 contiguous rows of the pool; a box is 16 rows of 64 columns,
+//     one 128-byte swizzle span, so head size 128 takes two boxes per granule): 8 key granules and
+//     8 value granules per stage of 128 keys into a ring of STAGES stages, each signalled by
+//     an mbarrier; it runs ahead across item boundaries, so the ring(s) of an SM keep about
 //     130-190 KB on their way, and no thread computes an address per 16 bytes;
 //   * eight consumer warps take 16 keys of a stage each (scores and the second product on
 //     mma.sync as in the other kernel, softmax statistics in fp32, running over the item's
 //     stages), hand the stage back, and at the end of an item combine into one partial result.
-// Query rows of an item are one contiguous run of G * 64 values: one bulk copy.
+// Query rows of an item are one contiguous run of G * head_dim values: one bulk copy.
 //
 // All waits are bounded (see gemv_stream.cu).  Formula: src/model/sdpa.cpp:71-95.
 #include "common.cuh"
@@ -24,12 +26,8 @@
 namespace {
 
 constexpr int CW = 8;                   // consumer warps
-constexpr int HD = 64;
 constexpr int TILE = 128;               // keys per stage: 8 granules of 16
-constexpr int GRAN_BYTES = 16 * HD * 2; // 2 KB: 16 rows of 128 bytes
-constexpr int STAGE_BYTES = 2 * 8 * GRAN_BYTES;   // keys then values: 32 KB
-constexpr int STAGES = 3;                // per block; two blocks share an SM
-constexpr int Q_BYTES = 16 * HD * 2;
+constexpr int BOX_BYTES = 16 * 64 * 2;  // 2 KB: 16 rows of one 128-byte span
 constexpr int MIN_SPLIT_KEYS = 512, MAX_SPLIT_KEYS = 2048;   // keys per work item: chosen per launch
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr unsigned WAIT_LIMIT = 1u << 24;
@@ -121,16 +119,21 @@ __device__ __forceinline__ Item make_item(int item, int max_splits, int groups, 
   return it;
 }
 
+template <int HD, int STAGES>
 __global__ void __launch_bounds__((CW + 1) * 32)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __nv_bfloat16* __restrict__ q, float* __restrict__ part_o, float* __restrict__ part_ml,
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_of_token, PagedView pv,
                        int n_heads, int n_tokens, float scale_log2, int window, int max_splits, int comb_rows,
                        int split_keys, int* __restrict__ status) {
+  constexpr int HALVES = HD / 64;                   // spans of 64 columns per row of the cache
+  constexpr int GRAN_BYTES = HALVES * BOX_BYTES;    // a granule: [span][16 rows][128 bytes]
+  constexpr int STAGE_BYTES = 2 * 8 * GRAN_BYTES;   // 8 key granules, then 8 value granules
+  constexpr int Q_BYTES = 16 * HD * 2;
   extern __shared__ unsigned char raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
-  unsigned char* ring = smem;                                             // [STAGES][K 8 x 2 KB | V 8 x 2 KB]
-  unsigned char* q_s = smem + STAGES * STAGE_BYTES;                       // [2][16][64] bf16
+  unsigned char* ring = smem;                                             // [STAGES][K 8 granules | V 8 granules]
+  unsigned char* q_s = smem + STAGES * STAGE_BYTES;                       // [2][16][HD] bf16
   float* comb = reinterpret_cast<float*>(q_s + 2 * Q_BYTES);              // [CW][comb_rows][HD + 2]: m, l, o[HD]
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(comb + CW * comb_rows * (HD + 2));
   int* last_flag = reinterpret_cast<int*>(bars + 2 * STAGES + 4);
@@ -219,22 +222,23 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             issue_q();
             q_done = true;
           }
-          // lanes 0..7: the key box of granule `lane`; lanes 8..15: its value box
-          const int gran = lane & 7;
+          // lanes 0 .. 8 HALVES - 1: the key boxes (span lane / 8 of granule lane % 8); the next
+          // 8 HALVES lanes: the value boxes
+          const int gran = lane & 7, half = (lane >> 3) % HALVES, is_v = lane / (8 * HALVES);
           const int gi = (tile * TILE - w.split * split_keys) / 16 + gran;           // granule of the split
           const int j = gi >> 5;                                                       // the same for the tile's 8
           const int mine = j == 0 ? row[0] : (j == 1 ? row[1] : (j == 2 ? row[2] : row[3]));
           const int box_row = __shfl_sync(0xffffffffu, mine, gi & 31);                 // from who looked it up
-          const bool valid = lane < 16 && box_row >= 0;
+          const bool valid = lane < 16 * HALVES && box_row >= 0;
           const unsigned n_valid = __popc(__ballot_sync(0xffffffffu, valid));
           if (lane == 0) {
             if (round > 0) mbar_wait(empty0 + 8 * s, (round - 1) & 1, status, 22);
-            mbar_expect_tx(full0 + 8 * s, n_valid * GRAN_BYTES);
+            mbar_expect_tx(full0 + 8 * s, n_valid * BOX_BYTES);
           }
           __syncwarp();
           if (valid) {
-            const unsigned dst = ring_u + s * STAGE_BYTES + (lane >> 3) * 8 * GRAN_BYTES + gran * GRAN_BYTES;
-            tma_load_2d(dst, lane < 8 ? &map_k : &map_v, 0, box_row, full0 + 8 * s);
+            const unsigned dst = ring_u + s * STAGE_BYTES + is_v * 8 * GRAN_BYTES + gran * GRAN_BYTES + half * BOX_BYTES;
+            tma_load_2d(dst, is_v ? &map_v : &map_k, half * 64, box_row, full0 + 8 * s);
           }
         }
         if (!q_done) {
@@ -292,8 +296,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 #pragma unroll
         for (int kk = 0; kk < HD / 16; kk++) {
           unsigned b[4];
-          const int key = (mi >> 1) * 8 + r8, piece = kk * 2 + (mi & 1);
-          ldmatrix_x4(b, k_box + key * 128 + ((piece ^ (key & 7)) << 4));
+          const int key = (mi >> 1) * 8 + r8, piece = (kk & 3) * 2 + (mi & 1);
+          ldmatrix_x4(b, k_box + (kk >> 2) * BOX_BYTES + key * 128 + ((piece ^ (key & 7)) << 4));
           mma_bf16(sc[0], qa[kk], b[0], b[1]);
           mma_bf16(sc[1], qa[kk], b[2], b[3]);
         }
@@ -348,8 +352,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           // probability is exactly 0, but 0 x NaN would still poison the product, so clear them
           for (int r = 0; r < 16; r++) {
             const int key = w_begin + r;
-            if ((key < w.lo || key > w.pos) && lane < 8)
-              asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(v_box + r * 128 + lane * 16), "r"(0u) : "memory");
+            if ((key < w.lo || key > w.pos) && lane < 8 * HALVES)
+              asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n"
+                           ::"r"(v_box + (lane >> 3) * BOX_BYTES + r * 128 + (lane & 7) * 16), "r"(0u) : "memory");
           }
           asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
           __syncwarp();
@@ -363,8 +368,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 #pragma unroll
         for (int d = 0; d < HD / 8; d += 2) {
           unsigned b[4];
-          const int key = (mi & 1) * 8 + r8, piece = d + (mi >> 1);
-          ldmatrix_x4_trans(b, v_box + key * 128 + ((piece ^ (key & 7)) << 4));
+          const int key = (mi & 1) * 8 + r8, piece = (d & 7) + (mi >> 1);
+          ldmatrix_x4_trans(b, v_box + (d >> 3) * BOX_BYTES + key * 128 + ((piece ^ (key & 7)) << 4));
           mma_bf16(o[d], a, b[0], b[1]);
           mma_bf16(o[d + 1], a, b[2], b[3]);
         }
@@ -446,30 +451,33 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
 int g_merge_inside = 1;
 
-// Launches the first kernel of the decode attention for head size 64 (the merge kernel of
-// attention_decode.cu follows it).  Returns MF_ERR_BAD_ARG when this path does not apply.
-int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
-                      __nv_bfloat16* out, float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv,
-                      long long pool_rows, const int* positions, const int* seq_of_token, float scale, int window,
-                      int max_ctx, int* status, int* split_out, int* merged_out, cudaStream_t stream) {
-  if (pv.head_dim != HD || pv.page_size % 16) return MF_ERR_BAD_ARG;
+namespace {
+
+template <int HD, int STAGES, int BLOCKS_PER_SM>
+int launch_for(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, __nv_bfloat16* out,
+               float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv, long long pool_rows,
+               const int* positions, const int* seq_of_token, float scale, int window, int max_ctx, int* status,
+               int* split_out, int* merged_out, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = 2 * 8 * (HD / 64) * BOX_BYTES, Q_BYTES = 16 * HD * 2;
   CUtensorMap mk, mv;
-  int rc = tma_host::bf16_map(k_pool, pool_rows, HD, 16, HD, &mk);
+  int rc = tma_host::bf16_map(k_pool, pool_rows, HD, 16, 64, &mk);
   if (rc) return rc;
-  rc = tma_host::bf16_map(v_pool, pool_rows, HD, 16, HD, &mv);
+  rc = tma_host::bf16_map(v_pool, pool_rows, HD, 16, 64, &mv);
   if (rc) return rc;
   const int G0 = n_heads / pv.n_kv_heads;
   const int comb_rows = G0 < 16 ? G0 : 16;
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 2 * Q_BYTES + (size_t)CW * comb_rows * (HD + 2) * 4 + (2 * STAGES + 4) * 8 + 8 + 1024;
+  if (smem > 227 * 1024) return MF_ERR_BAD_ARG;       // the caller takes another kernel
   static DeviceOnce once;
   const int dev_ = mf_current_device();
   const int n_sms = mf_sm_count();
   if (dev_ < 0 || n_sms <= 0) return MF_ERR_BAD_ARG;
   if (!once.done[dev_]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
     once.done[dev_] = true;
   }
+  const int slots = BLOCKS_PER_SM * n_sms;
   // Longer splits cost less per key (an item ends with a combine of the eight warps), shorter
   // ones give more items: take the longest split that still gives most blocks an item.
   const int G = n_heads / pv.n_kv_heads, hgroups = (G + 15) / 16;
@@ -477,12 +485,12 @@ int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
   long long n_items = 0;
   for (;; split_keys /= 2) {
     n_items = (long long)n_tokens * pv.n_kv_heads * hgroups * ((max_ctx + split_keys - 1) / split_keys);
-    if (split_keys == MIN_SPLIT_KEYS || n_items * 20 >= (long long)2 * n_sms * 17) break;
+    if (split_keys == MIN_SPLIT_KEYS || n_items * 20 >= (long long)slots * 17) break;
   }
   *split_out = split_keys;
   const int max_splits = (max_ctx + split_keys - 1) / split_keys;
   if (n_items > 0x7fffffff) return MF_ERR_BAD_ARG;
-  const int grid = n_items < 2 * n_sms ? (int)n_items : 2 * n_sms;
+  const int grid = n_items < slots ? (int)n_items : slots;
   // the merge inside this kernel, where the tickets reach (g_merge_inside: for measurements)
   // Every item pays for its ticket (a fence and two barriers of the consumer warps), the merge kernel
   // costs one launch: with more than two items to a block the kernel of its own is the cheaper way
@@ -490,9 +498,34 @@ int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const
   const bool inside = g_merge_inside && (long long)n_tokens * pv.n_kv_heads * hgroups <= MAX_TICKETS &&
                       n_items <= 2ll * grid;
   *merged_out = inside ? 1 : 0;
-  return (int)launch_dep(attn_decode_tma_kernel, dim3(grid), dim3((CW + 1) * 32), smem, stream, mk, mv, q, part_o,
+  return (int)launch_dep(attn_decode_tma_kernel<HD, STAGES>, dim3(grid), dim3((CW + 1) * 32), smem, stream, mk, mv, q, part_o,
                          part_ml, inside ? out : (__nv_bfloat16*)nullptr, positions, seq_of_token, pv, n_heads, n_tokens, scale * LOG2E, window, max_splits,
                          comb_rows, split_keys, status);
+}
+
+}  // namespace
+
+// Launches the first kernel of the decode attention for head sizes 64 and 128 (the merge kernel of
+// attention_decode.cu follows it unless *merged_out says that it merged its splits itself).
+// Returns MF_ERR_BAD_ARG when this path does not apply.
+int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
+                      __nv_bfloat16* out, float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv,
+                      long long pool_rows, const int* positions, const int* seq_of_token, float scale, int window,
+                      int max_ctx, int* status, int* split_out, int* merged_out, cudaStream_t stream) {
+  if (pv.page_size % 16) return MF_ERR_BAD_ARG;
+  if (pv.head_dim == 64)
+    return launch_for<64, 3, 2>(q, k_pool, v_pool, out, part_o, part_ml, n_tokens, n_heads, pv, pool_rows, positions,
+                                seq_of_token, scale, window, max_ctx, status, split_out, merged_out, stream);
+  if (pv.head_dim == 128) {
+    // one block per SM with three stages of 64 KB; groups of many heads need a combine buffer that
+    // leaves room for two stages only
+    const int rc = launch_for<128, 3, 1>(q, k_pool, v_pool, out, part_o, part_ml, n_tokens, n_heads, pv, pool_rows,
+                                         positions, seq_of_token, scale, window, max_ctx, status, split_out, merged_out, stream);
+    if (rc != MF_ERR_BAD_ARG) return rc;
+    return launch_for<128, 2, 1>(q, k_pool, v_pool, out, part_o, part_ml, n_tokens, n_heads, pv, pool_rows, positions,
+                                 seq_of_token, scale, window, max_ctx, status, split_out, merged_out, stream);
+  }
+  return MF_ERR_BAD_ARG;
 }
 
 // After a kernel of this file gave up a bounded wait its tickets may be left counting: the next

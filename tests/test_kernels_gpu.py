@@ -205,16 +205,21 @@ def test_attention_generic(case, dtype):
                                                (8, 2, 64, [5000, 4097, 2048, 2049, 300], 0),
                                                (8, 2, 64, [5000, 2300, 640], 2500),
                                                (8, 8, 64, [600 + 7 * i for i in range(30)], 0),    # two items to a block
-                                               (8, 8, 64, [600 + 7 * i for i in range(44)], 0)])   # more: merge kernel
+                                               (8, 8, 64, [600 + 7 * i for i in range(44)], 0),    # more: merge kernel
+                                               # head size 128: two boxes per granule, one block per SM
+                                               (8, 2, 128, [3000, 700, 45], 0), (24, 8, 128, [5000, 2300, 640], 2500),
+                                               (12, 4, 128, [600 + 7 * i for i in range(20)], 0),
+                                               (16, 1, 128, [900, 40, 1], 300),                    # 16 heads to a group: two stages
+                                               (8, 8, 128, [600 + 7 * i for i in range(44)], 0)])
 def test_attention_decode(case, tma):
-    """Head size 64 has the TMA kernel, which merges its splits itself (the block that finishes a
+    """Head sizes 64 and 128 have the TMA kernel, which merges its splits itself (the block that finishes a
     group's last split; run twice here: the tickets must be back at zero) or leaves them to the
     merge kernel, and the kernel without tensor copies."""
     import torch
     from mlxforge_b200.csrc import ops
     nh, nkv, hd, lengths, window = case
-    if tma != "tma" and hd != 64:
-        pytest.skip("only head size 64 has more than one kernel")
+    if tma != "tma" and hd not in (64, 128):
+        pytest.skip("only head sizes 64 and 128 have more than one kernel")
     old = ops.set_decode_tma(tma != "no tma")
     old_merge = ops.set_decode_merge_inside(tma == "tma")
     try:
@@ -309,6 +314,8 @@ DECISIVE_KERNELS = {
     "decode tensor copies, merge kernel": (64, False, True, True, False),
     "decode 64 without tensor copies": (64, False, True, False, True),
     "decode 128": (128, False, True, True, True),
+    "decode 128, merge kernel": (128, False, True, True, False),
+    "decode 128 without tensor copies": (128, False, True, False, True),
 }
 
 

@@ -120,10 +120,10 @@ MUST_RUN = {
     ("E", "mixed"): ["attn_prefill_tc", "attn_prefill_mma", ("attn_decode_tma", "attn_decode_tma_merged"), "stream_tmap"],
     ("E", "mixed_tight"): ["attn_prefill_mma", ("attn_decode_tma", "attn_decode_tma_merged")],
     ("F", "whole"): ["attn_prefill_tc", "gemm_tc_swiglu"],
-    ("F", "decode_tail"): ["attn_prefill_tc", ("attn_decode", "attn_decode_tma", "attn_decode_tma_merged"), "stream_tmap"],
+    ("F", "decode_tail"): ["attn_prefill_tc", ("attn_decode_tma", "attn_decode_tma_merged"), "stream_tmap"],
     ("F", "portions"): ["attn_prefill_tc", "attn_prefill_mma", "gemm_tc_swiglu"],
-    ("F", "mixed"): ["attn_prefill_mma", ("attn_decode", "attn_decode_tma", "attn_decode_tma_merged")],
-    ("F", "mixed_tight"): ["attn_prefill_mma", ("attn_decode", "attn_decode_tma", "attn_decode_tma_merged")],
+    ("F", "mixed"): ["attn_prefill_mma", ("attn_decode_tma", "attn_decode_tma_merged")],
+    ("F", "mixed_tight"): ["attn_prefill_mma", ("attn_decode_tma", "attn_decode_tma_merged")],
 }
 
 
