@@ -260,6 +260,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
   // -------------------------------------------------------------- consumers
   const int g = lane >> 2, tq = lane & 3;
+  // one split per group (every context of the launch fits into one): an item's result is the
+  // output, so it is stored at once and neither partial results nor tickets are needed
+  const bool direct = max_splits == 1 && out != nullptr;
   unsigned it = 0, live_items = 0;
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     const Item w = make_item(item, max_splits, groups, hgroups, G, positions, seq_of_token, window, split_keys);
@@ -404,6 +407,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         L += comb[(cw * CR + r) * CS + 1] * f;
         acc += comb[(cw * CR + r) * CS + 2 + d] * f;
       }
+      if (direct) {
+        // the only split of its group: what a merge of one split would compute, acc * 2^0 / (L * 2^0)
+        out[((long long)w.t * n_heads + w.head0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
+        continue;
+      }
       const long long row = ((long long)w.t * n_heads + w.head0 + r) * max_splits + w.split;
       part_o[row * HD + d] = acc;
       if (d == 0) {
@@ -411,7 +419,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         part_ml[row * 2 + 1] = L;
       }
     }
-    if (out == nullptr) {
+    if (out == nullptr || direct) {
       consumer_sync();     // `comb` is free for the next item
       continue;
     }
