@@ -498,6 +498,13 @@ int launch_for(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_b
   *split_out = split_keys;
   const int max_splits = (max_ctx + split_keys - 1) / split_keys;
   if (n_items > 0x7fffffff) return MF_ERR_BAD_ARG;
+  // One block per SM has nobody beside it to stream while it combines, writes and hands in an item's
+  // result, and items are dealt out in turn, not by size: with many items of unequal contexts to a
+  // block (64 requests of 128 to 4352 tokens: a serving run's decode steps took 11.7 ms instead of
+  // 6.6) the kernel without tensor copies, whose many small blocks the hardware deals out, is the
+  // faster one.  Up to two items a block this one is (62 against 68 us at 8 x 8192, 15 against 21 us
+  // at 1 x 8192 on the 3B shape).
+  if (BLOCKS_PER_SM == 1 && n_items > 2ll * slots) return MF_ERR_BAD_ARG;
   const int grid = n_items < slots ? (int)n_items : slots;
   // the merge inside this kernel, where the tickets reach (g_merge_inside: for measurements)
   // Every item pays for its ticket (a fence and two barriers of the consumer warps), the merge kernel
