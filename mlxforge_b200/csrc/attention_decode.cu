@@ -361,7 +361,7 @@ int launch_decode(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __n
 int launch_decode_tma(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
                       __nv_bfloat16* out, float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv,
                       long long pool_rows, const int* positions, const int* seq_of_token, float scale, int window,
-                      int max_ctx, int* status, int* split_out, int* merged_out, cudaStream_t stream);
+                      int max_ctx, int unequal, int* status, int* split_out, int* merged_out, cudaStream_t stream);
 extern int g_merge_inside;
 
 static int g_decode_tma = 1;
@@ -387,6 +387,11 @@ MF_API int mf_set_decode_tma(int on, int* status) {
   g_decode_status = status;
   return old;
 }
+// The status word alone; the on/off setting stays as it is.
+MF_API int mf_set_decode_status(int* status) {
+  g_decode_status = status;
+  return 0;
+}
 
 // Fewest keys per split for a head size: the caller sizes the scratch with it (a launch may
 // choose longer splits and then uses less).
@@ -398,10 +403,13 @@ MF_API int mf_attention_decode_split(int hd) {
 // Scratch: part_o  [n_tokens * n_heads * max_splits * hd] floats,
 //          part_ml [n_tokens * n_heads * max_splits * 2] floats, max_splits = ceil(max_ctx / split).
 // `max_ctx` bounds position + 1 of every token; a larger value only costs idle blocks.
-MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_o,
-                               float* part_ml, int n_tokens, int n_heads, int n_kv, int hd, const int* positions,
-                               const int* seq_of_token, const int* block_table, int bt_stride, int page_size,
-                               float scale, int window, int max_ctx, cudaStream_t stream) {
+// `unequal_contexts` != 0: the caller knows that the tokens' contexts differ widely in length (the
+// kernels read the lengths on the device, the launcher cannot); with many work items to a block
+// the kernel whose blocks the hardware deals out is then taken instead of the persistent one.
+MF_API int mf_attention_decode_hinted(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_o,
+                                      float* part_ml, int n_tokens, int n_heads, int n_kv, int hd, const int* positions,
+                                      const int* seq_of_token, const int* block_table, int bt_stride, int page_size,
+                                      float scale, int window, int max_ctx, int unequal_contexts, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (hd < 16 || hd > 256 || hd % 16 || n_kv <= 0 || n_heads % n_kv || max_ctx <= 0) return MF_ERR_BAD_ARG;
   if (n_tokens > 65535) return MF_ERR_BAD_ARG;
@@ -414,7 +422,8 @@ MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_
     // the map's row count only bounds the unit's own range check; rows beyond the pool are never asked for
     int split = SPLIT_KEYS, merged = 0;
     const int rc = launch_decode_tma(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, 1ll << 28, positions,
-                                     seq_of_token, scale, window, max_ctx, g_decode_status, &split, &merged, stream);
+                                     seq_of_token, scale, window, max_ctx, unequal_contexts, g_decode_status, &split,
+                                     &merged, stream);
     if (rc == 0 && merged) {
       mf_count(MF_K_ATTN_DECODE_TMA_MERGED);
       g_last_decode_launches = 1;
@@ -438,6 +447,14 @@ MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_
                               scale, window, max_ctx, stream);
   return launch_decode<256>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token, scale,
                             window, max_ctx, stream);
+}
+
+MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_o,
+                               float* part_ml, int n_tokens, int n_heads, int n_kv, int hd, const int* positions,
+                               const int* seq_of_token, const int* block_table, int bt_stride, int page_size,
+                               float scale, int window, int max_ctx, cudaStream_t stream) {
+  return mf_attention_decode_hinted(q, k_pool, v_pool, out, part_o, part_ml, n_tokens, n_heads, n_kv, hd, positions,
+                                    seq_of_token, block_table, bt_stride, page_size, scale, window, max_ctx, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -29,6 +29,7 @@ _SIGNATURES = {
     "mf_sample": [_P, c_int, c_int, c_longlong, _P, _P, _P, _P],
     "mf_set_pdl": [c_int],
     "mf_set_decode_tma": [c_int, _P],
+    "mf_set_decode_status": [_P],
     "mf_set_decode_merge_inside": [c_int],
     "mf_attention_decode_launches": [],
     "mf_gemm_bf16": [_P, _P, _P, c_int, c_int, c_int, c_int, _P, _P],
@@ -41,6 +42,8 @@ _SIGNATURES = {
     "mf_attention_decode_split": [c_int],
     "mf_attention_decode": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,
                             c_float, c_int, c_int, _P],
+    "mf_attention_decode_hinted": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,
+                                   c_float, c_int, c_int, c_int, _P],
     "mf_apply_penalties": [_P, c_int, c_longlong, _P, _P, _P, _P, _P, _P, _P],
     "mf_filter_logits": [_P, c_int, c_int, c_longlong, _P, _P, _P, _P, _P],
     "mf_kernel_kinds": [],

@@ -278,25 +278,28 @@ def attention_decode_scratch(n_tokens: int, n_heads: int, head_dim: int, max_ctx
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                      part_o: torch.Tensor, part_ml: torch.Tensor, positions: torch.Tensor,
                      seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int, n_heads: int,
-                     n_kv: int, head_dim: int, scale: float, window: int, max_ctx: int) -> None:
+                     n_kv: int, head_dim: int, scale: float, window: int, max_ctx: int,
+                     unequal_contexts: bool = False) -> None:
     """Attention of tokens that are each the newest of their sequence (one query per
     sequence), bfloat16, split over the keys; ``part_o`` / ``part_ml`` are float32
-    scratch of at least ``attention_decode_scratch`` elements."""
+    scratch of at least ``attention_decode_scratch`` elements.  ``unequal_contexts``: the
+    caller knows that the contexts differ widely in length (see mf_attention_decode_hinted)."""
     _need_cuda(q, k_pool, v_pool, out, part_o, part_ml, positions, seq_of_token, block_table)
     if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
         raise KernelError("attention_decode: bfloat16 only")
     n = q.shape[0]
     global _TMA_STATUS_SET
     if not _TMA_STATUS_SET:
-        library().mf_set_decode_tma(1, kernel_status(q.device).data_ptr())
+        library().mf_set_decode_status(kernel_status(q.device).data_ptr())
         _TMA_STATUS_SET = True
     need_o, need_ml = attention_decode_scratch(n, n_heads, head_dim, max_ctx)
     if part_o.numel() < need_o or part_ml.numel() < need_ml or part_o.dtype != torch.float32:
         raise KernelError("attention_decode: scratch too small")
-    check(library().mf_attention_decode(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
-                                        part_o.data_ptr(), part_ml.data_ptr(), n, n_heads, n_kv, head_dim,
-                                        positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
-                                        block_table.shape[1], page_size, scale, window, max_ctx, _stream()),
+    check(library().mf_attention_decode_hinted(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+                                               part_o.data_ptr(), part_ml.data_ptr(), n, n_heads, n_kv, head_dim,
+                                               positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
+                                               block_table.shape[1], page_size, scale, window, max_ctx,
+                                               1 if unequal_contexts else 0, _stream()),
           "attention_decode", launches=0)
     # one kernel when the TMA kernel merged its splits itself, two when a merge kernel followed
     count_launches(int(library().mf_attention_decode_launches()))

@@ -28,12 +28,16 @@ def paged_attention(rt, batch, q, lane, out, n_heads: int, scale: float, window:
     table = batch.block_table(lane.group)
     nd = batch.n_decode if q.dtype == torch.bfloat16 else 0
     if nd > 0:
+        # contexts of very unequal length (the host knows them, the launcher does not): said to the
+        # kernel's launcher, which then avoids dealing many items of unequal size out in turn
+        lens = batch.ctx_len[:nd]
+        unequal = nd >= 8 and max(lens) * nd > 1.3 * sum(lens)
         n_o, n_ml = ops.attention_decode_scratch(nd, n_heads, need.head_dim, batch.max_ctx)
         ops.attention_decode(q[:nd], lane.k, lane.v, out[:nd],
                              rt.buffer("attn.part_o", (n_o,), torch.float32),
                              rt.buffer("attn.part_ml", (n_ml,), torch.float32),
                              batch.positions[:nd], batch.seq_of_token[:nd], table, lane.page_size, n_heads,
-                             need.n_kv_heads, need.head_dim, scale, window, batch.max_ctx)
+                             need.n_kv_heads, need.head_dim, scale, window, batch.max_ctx, unequal)
     if nd < batch.n_tokens and q.dtype == torch.bfloat16:
         ops.attention_prefill(q, lane.k, lane.v, out, batch.seq_q_start[nd:], batch.seq_q_len[nd:],
                               batch.seq_ctx_len[nd:], nd, max(batch.q_len[nd:]), table, lane.page_size,
