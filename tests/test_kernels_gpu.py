@@ -200,8 +200,7 @@ def test_attention_generic(case, dtype):
         assert np.max(np.abs(got[i] - want)) < tol, (i, s, p)
 
 
-@pytest.mark.parametrize("tma", ["tma", "tma, merge kernel", "no tma"])
-@pytest.mark.parametrize("case", ATTN_CASES + [(32, 8, 64, [2100, 700, 1, 513, 512], 0), (4, 1, 64, [900, 40], 300),
+DECODE_CASES = ATTN_CASES + [(32, 8, 64, [2100, 700, 1, 513, 512], 0), (4, 1, 64, [900, 40], 300),
                                                (8, 2, 64, [5000, 4097, 2048, 2049, 300], 0),
                                                (8, 2, 64, [5000, 2300, 640], 2500),
                                                (8, 8, 64, [600 + 7 * i for i in range(30)], 0),    # two items to a block
@@ -210,7 +209,12 @@ def test_attention_generic(case, dtype):
                                                (8, 2, 128, [3000, 700, 45], 0), (24, 8, 128, [5000, 2300, 640], 2500),
                                                (12, 4, 128, [600 + 7 * i for i in range(20)], 0),
                                                (16, 1, 128, [900, 40, 1], 300),                    # 16 heads to a group: two stages
-                                               (8, 8, 128, [600 + 7 * i for i in range(44)], 0)])
+                                               (8, 8, 128, [600 + 7 * i for i in range(44)], 0)]
+# head sizes 64 and 128 have three forms of the kernel; the others one
+DECODE_FORMS = [(c, f) for c in DECODE_CASES for f in (("tma", "tma, merge kernel", "no tma") if c[2] in (64, 128) else ("tma",))]
+
+
+@pytest.mark.parametrize("case,tma", DECODE_FORMS)
 def test_attention_decode(case, tma):
     """Head sizes 64 and 128 have the TMA kernel, which merges its splits itself (the block that finishes a
     group's last split; run twice here: the tickets must be back at zero) or leaves them to the
@@ -218,8 +222,6 @@ def test_attention_decode(case, tma):
     import torch
     from mlxforge_b200.csrc import ops
     nh, nkv, hd, lengths, window = case
-    if tma != "tma" and hd not in (64, 128):
-        pytest.skip("only head sizes 64 and 128 have more than one kernel")
     old = ops.set_decode_tma(tma != "no tma")
     old_merge = ops.set_decode_merge_inside(tma == "tma")
     try:
