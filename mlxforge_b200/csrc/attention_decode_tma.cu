@@ -441,13 +441,31 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       for (int i = threadIdx.x; i < w.n_rows * HD; i += CW * 32) {
         const int r = i / HD, d = i - r * HD;
         const long long row = ((long long)w.t * n_heads + w.head0 + r) * max_splits + s0;
-        float M = -INFINITY;
-        for (int sp = 0; sp < n_live; sp++) M = fmaxf(M, __ldcg(part_ml + (row + sp) * 2));
-        float L = 0.f, acc = 0.f;
-        for (int sp = 0; sp < n_live; sp++) {
-          const float f = exp2f(__ldcg(part_ml + (row + sp) * 2) - M);
-          L += __ldcg(part_ml + (row + sp) * 2 + 1) * f;
-          acc += __ldcg(part_o + (row + sp) * HD + d) * f;
+        // eight splits' statistics and values are fetched at once (their addresses do not depend on
+        // one another: one round trip through L2 instead of one per split), then added in order
+        float M = -INFINITY, L = 0.f, acc = 0.f;
+        for (int s8 = 0; s8 < n_live; s8 += 8) {
+          float pm[8], pl[8], po[8];
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const bool in = s8 + j < n_live;
+            pm[j] = in ? __ldcg(part_ml + (row + s8 + j) * 2) : -INFINITY;
+            pl[j] = in ? __ldcg(part_ml + (row + s8 + j) * 2 + 1) : 0.f;
+            po[j] = in ? __ldcg(part_o + (row + s8 + j) * HD + d) : 0.f;
+          }
+          float M8 = M;
+#pragma unroll
+          for (int j = 0; j < 8; j++) M8 = fmaxf(M8, pm[j]);
+          const float keep = (M == -INFINITY) ? 0.f : exp2f(M - M8);     // what was summed so far, on the new scale
+          L *= keep;
+          acc *= keep;
+          M = M8;
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const float f = (pm[j] == -INFINITY) ? 0.f : exp2f(pm[j] - M);
+            L += pl[j] * f;
+            acc += po[j] * f;
+          }
         }
         out[((long long)w.t * n_heads + w.head0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
       }
