@@ -7,10 +7,15 @@ safetensors reader, its own config reading and its own sampler.
 
 The reference's model code needs Apple MLX (``CMakeLists.txt:14-16`` refuses
 other hosts, every model source includes ``mlx/...``), so it cannot be imported
-or compiled here and this file rests on the formulas.  Two of the reference's
-committed fixtures need no weights and anchor the position encoding:
-``reference/fixtures/rope_freqs.npy`` and ``q_pre0.npy -> q_rope0.npy``; small
-copies of what they check are under ``tests/golden/``.
+or compiled here and this file rests on the formulas.  Three of the reference's
+committed fixtures need no weights: ``reference/fixtures/rope_freqs.npy`` and
+``q_pre0.npy -> q_rope0.npy`` anchor the position encoding, ``embeddings.npy ->
+attn_norm0.npy`` the RMSNorm (its weight is the same vector for every position);
+small copies of what they check are under ``tests/golden/`` with the scripts that
+cut them, and ``tests/test_plain.py`` holds this file against them.  The one part
+of the reference that does compile here, its configuration parser, is compared
+with this build's parser in ``tests/test_config_reference.py``.  Attention and the
+feed-forward have no fixture without weights and stay pinned by their formulas.
 """
 from __future__ import annotations
 
