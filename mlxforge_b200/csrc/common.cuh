@@ -89,12 +89,18 @@ __device__ __forceinline__ long long granule_offset(const PagedView& pv, int seq
 
 // ---------------------------------------------------------------------------- dependent launch
 // Kernels of the decode step are launched so that the next kernel may start while this
-// one is still running (programmatic dependent launch): a kernel does what needs no
-// input from its predecessor (fetching weights, which never change), waits for the
-// predecessor to finish (pdl_wait) and then lets its own dependents go (pdl_launch): they
-// start while this kernel runs, one kernel ahead and no further.  Every global
-// read of activations and every global write comes after pdl_wait, so the result is that of
-// running the kernels one after the other.  Under a normal launch both are no-ops.
+// one is still running (programmatic dependent launch).  A kernel lets its own dependents go
+// (pdl_launch), does what needs no input from its predecessor (fetching weights, which never
+// change, and keys that earlier steps wrote) and waits for the predecessor to finish (pdl_wait)
+// before it reads an activation or writes anything, so the result is that of running the
+// kernels one after the other.  The streamed products and the small kernels between them let
+// their dependents go FIRST: the blocks of the kernels that follow then take an SM's room the
+// moment a block of the running kernel leaves it and fill their rings while the rest of that
+// kernel and the small kernel after it finish (1.125 -> 1.095 ms for a decode step of batch 8).
+// A dependent starts only when every block of its predecessor has let it go, that is when all
+// of them are resident or done, so no kernel can wait for one that has no room to start.  The
+// first kernel of a step (the embedding) waits before it lets go: nothing of a step starts
+// before the step's inputs are in place.  Under a normal launch both are no-ops.
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 

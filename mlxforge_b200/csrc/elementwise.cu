@@ -98,8 +98,8 @@ add_rmsnorm_bf16_vec_kernel(float* __restrict__ resid, const __nv_bfloat16* __re
                             const float* __restrict__ w, float eps, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ rows, int H) {
   __shared__ float red[32];
+  pdl_launch();              // the product after this one fetches its weights meanwhile
   pdl_wait();
-  pdl_launch();
   const int r = blockIdx.x;
   const long long src = rows ? rows[r] : r;
   float* x = resid + src * H;
@@ -243,8 +243,8 @@ rope_kv_write_bf16_vec_kernel(const __nv_bfloat16* __restrict__ qkv, int n_heads
                               __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
                               int write_kv) {
   extern __shared__ float cs[];            // [half] cos, [half] sin
+  pdl_launch();              // the attention after this one fetches older keys and values meanwhile
   pdl_wait();
-  pdl_launch();
   const int t = blockIdx.x;
   const int pos = positions[t], seq = seq_of_token[t];
   const int half = rot >> 1;

@@ -96,6 +96,7 @@ stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   const unsigned ring_u = smem_u32(ring), bars_u = smem_u32(bars);
 
   if (threadIdx.x == 0) {
+    pdl_launch();            // the kernels after this one take an SM's room as blocks of this one leave
     for (int s = 0; s < STAGES; s++) {
       mbar_init(bars_u + 8 * s, 1);                  // full: the producer's arrive + the bytes
       mbar_init(bars_u + 8 * (STAGES + s), CW);      // empty: one arrive per consumer warp
@@ -132,7 +133,6 @@ stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   const int g = lane >> 2, t = lane & 3;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   pdl_wait();                // x comes from the kernel before this one
-  if (threadIdx.x == 0) pdl_launch();
   unsigned it = 0;
   for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
     const int n0 = tile * ROWS;
@@ -220,8 +220,7 @@ stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
 // the fragment reads off each other's banks: a thread takes the 16-byte pieces 2t and 2t+1 of
 // its warp's chunk, so the eight threads of a quarter-warp (rows g, g+1) touch eight different
 // pieces.  Needs K to be a whole number of stages; other widths take the kernel above.
-// Stages of the ring: four, or six where a product has so few tiles that its blocks do not fill
-// the device and each has to keep more on its way.
+// Stages of the ring: six (see dispatch()).
 constexpr int T_STAGE_BYTES = 16384;
 
 __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, int c0, int c1, int c2,
@@ -249,6 +248,7 @@ stream_tmap_kernel(const __nv_bfloat16* __restrict__ x, const __grid_constant__ 
   const unsigned ring_u = smem_u32(smem), bars_u = smem_u32(bars);
 
   if (threadIdx.x == 0) {
+    pdl_launch();            // the kernels after this one take an SM's room as blocks of this one leave
     for (int s = 0; s < T_STAGES; s++) {
       mbar_init(bars_u + 8 * s, 1);
       mbar_init(bars_u + 8 * (T_STAGES + s), CW);
@@ -275,7 +275,6 @@ stream_tmap_kernel(const __nv_bfloat16* __restrict__ x, const __grid_constant__ 
   const int g = lane >> 2, t = lane & 3;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   pdl_wait();                // x comes from the kernel before this one
-  if (threadIdx.x == 0) pdl_launch();
   unsigned it = 0;
   for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
     const int n0 = tile * ROWS;
@@ -421,19 +420,15 @@ int dispatch(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, i
   // (tiles beyond N here, rows of x beyond M in gemm_mid_rows.cu) are used again and again on one
   // barrier without fault.  Such widths take the row-segment copies.
   if (K % (small ? 1024 : 512) == 0 && g_stream_tensor_copies) {
-    // few tiles of many stages each: the blocks do not fill the device, so each keeps six stages on
-    // their way instead of four
-    const bool deep = small && (N + 7) / 8 <= 2 * n_sms && K >= 6 * 1024;
-    if (M <= 8) {
-      if (deep) return launch_tmap<1, 8, 6, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
-      return small ? launch_tmap<1, 8, 4, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream)
-                   : launch_tmap<1, 16, 4, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
-    }
-    if (M <= 16) {
-      if (deep) return launch_tmap<2, 8, 6, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
-      return small ? launch_tmap<2, 8, 4, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream)
-                   : launch_tmap<2, 16, 4, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
-    }
+    // Six stages of 16 KB, two blocks per SM: under load a copy takes 3 to 4 us to arrive, so an SM
+    // has to keep nearly all of its shared memory on the way (four stages: 1.141 ms for a decode step
+    // of batch 8, six: 1.133, and 1.102 against 1.117 once the kernels before let this one start early).
+    if (M <= 8)
+      return small ? launch_tmap<1, 8, 6, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream)
+                   : launch_tmap<1, 16, 6, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
+    if (M <= 16)
+      return small ? launch_tmap<2, 8, 6, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream)
+                   : launch_tmap<2, 16, 6, OutT>(x, W, out, M, N, K, mode, status, n_sms, stream);
     return MF_ERR_BAD_ARG;
   }
   if (M <= 8) {
