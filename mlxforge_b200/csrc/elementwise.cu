@@ -244,7 +244,8 @@ rope_kv_write_bf16_vec_kernel(const __nv_bfloat16* __restrict__ qkv, int n_heads
                               int write_kv) {
   extern __shared__ float cs[];            // [half] cos, [half] sin
   pdl_launch();              // the attention after this one fetches older keys and values meanwhile
-  pdl_wait();
+  // positions and the frequency table are in place before the step's first kernel starts and do not
+  // change during it: the angles are computed before the wait, off the path between two kernels
   const int t = blockIdx.x;
   const int pos = positions[t], seq = seq_of_token[t];
   const int half = rot >> 1;
@@ -255,6 +256,7 @@ rope_kv_write_bf16_vec_kernel(const __nv_bfloat16* __restrict__ qkv, int n_heads
     cs[half + j] = s;
   }
   __syncthreads();
+  pdl_wait();
   const int width = (n_heads + 2 * n_kv) * hd;
   const __nv_bfloat16* row = qkv + (long long)t * width;
   const int rc = half >> 3;                // 16-byte pieces of rotated pairs per head
