@@ -80,6 +80,10 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
 }
+// Between a thread's last read of a buffer that the copy engine fills and the arrival that hands it
+// back: the reads are generic-proxy accesses, the next copy an async-proxy write, and the mbarrier
+// alone does not order the one before the other (see gemv_stream.cu, where it was measured).
+__device__ __forceinline__ void stage_read_done() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CW * 32) : "memory"); }
 
 // One counter per (token, group of heads): every split of that group that saw keys takes a
@@ -275,6 +279,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 #pragma unroll
       for (int kk = 0; kk < HD / 16; kk++)
         ldmatrix_x4(qa[kk], q_u + b * Q_BYTES + (lane & 15) * (HD * 2) + (kk * 16 + (lane >> 4) * 8) * 2);
+      stage_read_done();
       __syncwarp();
       if (lane == 0) mbar_arrive(qempty0 + 8 * b);
     }
@@ -377,6 +382,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           mma_bf16(o[d + 1], a, b[2], b[3]);
         }
       }
+      stage_read_done();
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
     }

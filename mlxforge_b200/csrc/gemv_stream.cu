@@ -77,6 +77,12 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// Between a thread's last read of a stage and the arrival that hands the stage back.  The reads are
+// ordinary loads (generic proxy), the copy that overwrites the stage comes from the copy engine
+// (async proxy), and an mbarrier orders accesses within one proxy only: without this fence a lane
+// now and then read the NEXT copy's bytes (weights coded by tile and stage showed it: 16 rows of x,
+// 2048 x 8192, wrong in 595 of 600 launches, 17 of 600 at 16384 x 2048; with the fence 0 of 600).
+__device__ __forceinline__ void stage_read_done() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CW * 32) : "memory"); }
 
 template <int NB, int ROWS, typename OutT>
@@ -168,6 +174,7 @@ stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
           mma_bf16(acc[nb], a.z, b.z, a.w, b.w, xv[c][nb].z, xv[c][nb].w);
         }
       }
+      stage_read_done();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars_u + 8 * (STAGES + s));
     }
@@ -313,6 +320,7 @@ stream_tmap_kernel(const __nv_bfloat16* __restrict__ x, const __grid_constant__ 
           }
         }
       }
+      stage_read_done();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars_u + 8 * (T_STAGES + s));
     }

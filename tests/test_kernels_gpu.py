@@ -476,6 +476,32 @@ def test_mid_linear_swiglu(M, I, K):
         assert np.max(np.abs(host(out) - want)) < 2.0 ** -6 * max(1.0, np.abs(want).max())
 
 
+@pytest.mark.parametrize("M,N,K", [(16, 2048, 8192), (16, 16384, 2048), (8, 16384, 2048), (12, 16384, 3072), (16, 28672, 4096)])
+def test_stream_linear_reads_a_stage_before_the_next_copy_lands(M, N, K):
+    """A stage of the ring is read by ordinary loads and overwritten by the copy engine: the reads must be
+    done before the stage is handed back.  Weights that say which tile and which quarter of K they come
+    from, rows of x that each pick one sixteenth of K, float32 sums of small integers: every output is
+    exact, and a lane that read the next copy's bytes shows as another tile's or quarter's value.  (Without
+    the proxy fence before the hand-back the first size was wrong in 595 of 600 launches.)"""
+    import torch
+    from mlxforge_b200.csrc import ops
+    k = torch.arange(K, device="cuda")
+    x = (k[None, :] // (K // 16) == torch.arange(M, device="cuda")[:, None]).to(torch.bfloat16)
+    n = torch.arange(N, device="cuda")
+    w = (((n[:, None] // 16) % 64) + 64 * (k[None, :] * 4 // K)).to(torch.bfloat16)        # at most 255: exact in bfloat16
+    want = x.double() @ w.double().T
+    out = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    for launch in range(60):
+        out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        ops.stream_linear(x, w, out)
+        torch.cuda.synchronize()
+        wrong = (out.double() != want).nonzero()
+        assert wrong.numel() == 0, (f"launch {launch}: {wrong.shape[0]} wrong sums, first at row {int(wrong[0, 0])} column "
+                                    f"{int(wrong[0, 1])}: {float(out[wrong[0, 0], wrong[0, 1]])} for {float(want[wrong[0, 0], wrong[0, 1]])}")
+    ops.check_kernel_status()
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 304, 80), (8, 2048, 2048), (5, 307, 136), (16, 96, 200), (9, 1000, 64),
                                    (3, 128256, 64), (8, 16, 8192), (2, 5000, 520), (7, 40, 1032), (16, 4737, 1536),
                                    (3, 9000, 512), (11, 4744, 1024), (8, 300, 3072), (13, 2050, 192), (8, 3000, 576),
