@@ -13,7 +13,7 @@
 //   * eight consumer warps wait for a buffer, read their 64-element slice of every row
 //     straight from it (rows are padded so that the 16-byte reads hit distinct banks),
 //     multiply, and hand the buffer back through a second mbarrier.
-// Two blocks run per SM.  Widths that are a whole number of stages take the second kernel of
+// Two blocks run per SM.  Widths that are whole spans of 64 columns take the second kernel of
 // this file, which brings a stage with one tensor copy instead of sixteen row-segment copies.
 //
 // The producer starts before the kernel that makes x has finished (weights never change);
@@ -226,7 +226,7 @@ stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
 // rows) is one stage, stored [chunk][row][128 bytes] with the 128-byte swizzle, which also keeps
 // the fragment reads off each other's banks: a thread takes the 16-byte pieces 2t and 2t+1 of
 // its warp's chunk, so the eight threads of a quarter-warp (rows g, g+1) touch eight different
-// pieces.  Needs K to be a whole number of stages; other widths take the kernel above.
+// pieces.  Needs K to be whole spans of 64 columns; other widths take the kernel above.
 // Stages of the ring: six (see dispatch()).
 constexpr int T_STAGE_BYTES = 16384;
 
@@ -418,16 +418,11 @@ int dispatch(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, i
   if (n_sms <= 0) return MF_ERR_BAD_ARG;
   // few output rows: tiles of 8 rows, so that there are blocks for every SM
   const bool small = mode == 0 && (N + 15) / 16 < 2 * n_sms;
-  // Tensor copies only where no box hangs over the end of the matrix along K (K a whole number of
-  // stages).  A 3-D box some of whose outermost slices (spans of 64 columns) lie wholly outside
-  // the tensor is not accounted for as a box that lies inside is: with K = 64 (seven of a box's
-  // eight spans outside) and a barrier that is used again for the next such box, stages were
-  // handed over with another tile's rows in them (3 x 128256 x 64 fails on its first call after a
-  // device-wide wait, so it is no ordering fault of the caller; the same shapes pass where every
-  // block has so few tiles that no barrier is used twice).  Boxes that hang over along the ROWS
-  // (tiles beyond N here, rows of x beyond M in gemm_mid_rows.cu) are used again and again on one
-  // barrier without fault.  Such widths take the row-segment copies.
-  if (K % (small ? 1024 : 512) == 0 && g_stream_tensor_copies) {
+  // Tensor copies for every width of whole 64-column spans; a box that hangs over the end of the
+  // matrix along K arrives with zeros there and counts its full size.  (Widths that are not whole
+  // stages were once kept off this path because 3 x 128256 x 64 gave wrong rows: that was the
+  // missing fence of stage_read_done(), which shows most where a block has many one-stage tiles.)
+  if (K % 64 == 0 && g_stream_tensor_copies) {
     // Six stages of 16 KB, two blocks per SM: under load a copy takes 3 to 4 us to arrive, so an SM
     // has to keep nearly all of its shared memory on the way (four stages: 1.141 ms for a decode step
     // of batch 8, six: 1.133, and 1.102 against 1.117 once the kernels before let this one start early).
