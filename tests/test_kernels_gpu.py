@@ -321,6 +321,55 @@ DECISIVE_KERNELS = {
 }
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+def test_decode_attention_reads_a_stage_before_the_next_copy_lands(hd):
+    """The decode attention's ring of keys and values is read by ordinary loads and refilled by the copy
+    engine, as the streamed products' ring is: with queries of zero every key weighs the same, the values
+    say which tile of 128 keys they belong to, and a granule of 16 values read from the copy that came
+    next moves the average by more than rounding does.  Many launches, eight sequences each.  (This kernel
+    has not been seen to fail without its fence, as the streamed product has; the test guards the ring.)"""
+    import torch
+    from mlxforge_b200.csrc import ops
+    n_seq, ctx, nh, nkv, page = 8, 1024, 8, 2, 16
+    pages_per_seq = ctx // page
+    n_pages = n_seq * pages_per_seq
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    order = torch.randperm(n_pages, generator=gen, device="cuda").to(torch.int32)
+    table = order.view(n_seq, pages_per_seq).contiguous()
+    k_pool = torch.randn((n_pages, nkv, page, hd), generator=gen, device="cuda").to(torch.bfloat16)
+    v_pool = torch.empty((n_pages, nkv, page, hd), dtype=torch.bfloat16, device="cuda")
+    key = torch.arange(ctx, device="cuda")
+    code = (((key // 128) % 7) * 32).to(torch.float32)                     # 0 .. 192 by tile of 128 keys
+    for s_ in range(n_seq):
+        for h in range(nkv):
+            vals = code + 8.0 * h + s_                                          # exact in bfloat16 (integers up to 215)
+            v_pool[table[s_].long(), h] = vals.view(pages_per_seq, page, 1).expand(-1, -1, hd).to(torch.bfloat16)
+    q = torch.zeros((n_seq, nh * hd), dtype=torch.bfloat16, device="cuda")
+    positions = torch.full((n_seq,), ctx - 1, dtype=torch.int32, device="cuda")
+    seq_of = torch.arange(n_seq, dtype=torch.int32, device="cuda")
+    n_o, n_ml = ops.attention_decode_scratch(n_seq, nh, hd, ctx)
+    part_o = torch.empty(n_o, dtype=torch.float32, device="cuda")
+    part_ml = torch.empty(n_ml, dtype=torch.float32, device="cuda")
+    want = torch.empty((n_seq, nh, hd), dtype=torch.float64, device="cuda")
+    for s_ in range(n_seq):
+        for h in range(nh):
+            want[s_, h] = float(code.double().mean()) + 8.0 * (h // (nh // nkv)) + s_
+    out = torch.empty((n_seq, nh * hd), dtype=torch.bfloat16, device="cuda")
+    from mlxforge_b200.csrc import binding
+    before = binding.kernel_launches()
+    for launch in range(60):
+        out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        ops.attention_decode(q, k_pool, v_pool, out, part_o, part_ml, positions, seq_of, table, page, nh, nkv, hd,
+                             hd ** -0.5, 0, ctx)
+        torch.cuda.synchronize()
+        err = (out.double().view(n_seq, nh, hd) - want).abs()
+        assert float(err.max()) < 0.6, f"launch {launch}: an average is off by {float(err.max()):.2f} (a stale granule moves it by 0.5 to 3)"
+    ops.check_kernel_status()
+    after = binding.kernel_launches()
+    assert (after["attn_decode_tma"] + after["attn_decode_tma_merged"]) - (before["attn_decode_tma"] + before["attn_decode_tma_merged"]) == 60
+
+
 @pytest.mark.parametrize("window", [0, 600])
 @pytest.mark.parametrize("kernel", list(DECISIVE_KERNELS))
 def test_one_key_decides_at_every_edge(kernel, window):
