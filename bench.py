@@ -347,6 +347,44 @@ def run_workload(args) -> int:
     return 0
 
 
+# Kinds of launches that `--without` leaves out of a decode step, to see what each costs inside it.
+LEFT_OUT = ("norms", "rotation", "attention", "qkv", "o", "gate_up", "down", "head", "products")
+
+
+def leave_out(kind: str, shape: dict) -> None:
+    """Replace the launcher of one kind of kernel by nothing (the step's numbers are then wrong and
+    only its time means something)."""
+    from mlxforge_b200.csrc import ops
+    hidden, inter = shape["hidden_size"], shape["intermediate_size"]
+    qkv_rows = (shape["num_attention_heads"] + 2 * shape["num_key_value_heads"]) * shape["head_dim"]
+    stream = ops.stream_linear
+
+    def nothing(*a, **k):
+        return None
+
+    def products(pred):
+        def f(x, w, out, swiglu=False):
+            return None if pred(w, swiglu) else stream(x, w, out, swiglu=swiglu)
+        return f
+
+    if kind == "norms":
+        ops.add_rmsnorm = nothing
+    elif kind == "rotation":
+        ops.rope_kv_write = nothing
+    elif kind == "attention":
+        ops.attention_decode = nothing
+    elif kind == "products":
+        ops.stream_linear = nothing
+    else:
+        pred = {"qkv": lambda w, s: not s and tuple(w.shape) == (qkv_rows, hidden),
+                "o": lambda w, s: not s and tuple(w.shape) == (hidden, shape["num_attention_heads"] * shape["head_dim"])
+                and tuple(w.shape) != (qkv_rows, hidden),
+                "gate_up": lambda w, s: s,
+                "down": lambda w, s: not s and tuple(w.shape) == (hidden, inter),
+                "head": lambda w, s: w.shape[0] == shape["vocab_size"]}[kind]
+        ops.stream_linear = products(pred)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -360,6 +398,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="decode / prefill: run just that part and print a short line (for profiling small cases)")
+    ap.add_argument("--without", default=None, choices=sorted(LEFT_OUT),
+                    help="with --only decode: time the step with the launches of one kind left out (its results are "
+                         "wrong; the difference to the full step is what that kind costs inside the step)")
     ap.add_argument("--workload", default="headline", choices=["headline", "serving", "longctx"],
                     help="serving: 64 requests on the 3B shape; longctx: 8 x 16,384 tokens on the 8B shape")
     args = ap.parse_args()
@@ -409,6 +450,11 @@ def main() -> int:
                           "layers": args.layers}))
         return 0
     BATCH_ = args.batch
+    if args.without:
+        if args.only != "decode":
+            print("--without goes with --only decode", file=sys.stderr)
+            return 2
+        leave_out(args.without, shape)
     clocks = ClockSampler()
     clocks.start()
     sec, launches, kv_tokens, pieces = decode_device(engine, BATCH_, ctx, args.steps, args.warmup)
@@ -417,9 +463,11 @@ def main() -> int:
     bytes_step = weight_bytes + kv_tokens * kv_per_token
     achieved = bytes_step / sec / 1e9
     if args.only == "decode":
-        print(json.dumps({"only": "decode", "shape": args.shape, "batch": BATCH_, "context": ctx, "layers": args.layers,
-                          "ms_per_step": round(sec * 1e3, 4), "launches_per_step": launches,
-                          "gbs": round(achieved, 1)}))
+        line = {"only": "decode", "shape": args.shape, "batch": BATCH_, "context": ctx, "layers": args.layers,
+                "ms_per_step": round(sec * 1e3, 4), "launches_per_step": launches, "gbs": round(achieved, 1)}
+        if args.without:
+            line = dict(line, without=args.without, gbs=None, note="a kind of kernel was left out: a timing, not a result")
+        print(json.dumps(line))
         return 0
 
     # the other batch sizes the metric names, at the headline context and at the 1024 tokens its
