@@ -73,3 +73,42 @@ def test_llama_1b_logits_in_every_cutting(llama_1b, tmp_path, dtype):
     else:
         # the decode steps: weights by one tensor copy per stage, attention by tensor copies
         assert ran["stream_tmap"] > 0 and ran["attn_decode_tma"] + ran["attn_decode_tma_merged"] > 0, ran
+
+
+def test_llama_1b_twelve_requests_decoding_together(llama_1b, tmp_path):
+    """Decode steps of 9 to 16 rows take the two-tile form of the streamed product (and the widest
+    matrices of this shape, 2048 x 8192 and 16384 x 2048, turn its ring over most often): twelve
+    requests decoding in one batch must each get the logits they get alone.  The plain implementation
+    is too slow for twelve more prompts of this size, so the engine alone is the reference here; that
+    path is held against the plain implementation by the test above."""
+    from mlxforge_b200.csrc import binding
+    from mlxforge_b200.engine.replay import make_runner, replay
+    d, cfg, _, _, tols = llama_1b
+    reqs = {f"r{i:02d}": random_prompt(cfg, 14 + (5 * i) % 17, 200 + i) for i in range(12)}
+    tail = 4
+    alone = TT.decode_tail(reqs, tail=tail)
+    together = TT.Trace()
+    for rid, toks in reqs.items():
+        head = len(toks) - tail
+        together.add([(rid, 0, toks[:head], [head - 1])])
+    for j in range(tail):
+        together.add([(rid, len(toks) - tail + j, toks[len(toks) - tail + j:len(toks) - tail + j + 1], [0])
+                      for rid, toks in reqs.items()], end=list(reqs) if j == tail - 1 else [])
+    runner = make_runner(d, "bfloat16", together.live_tokens_rounded(), max_seqs=len(reqs))
+    for pool in runner.cache._k + runner.cache._v:
+        pool.fill_(float("nan"))
+    replay(runner, alone.lines(), str(tmp_path / "alone"), done=io.StringIO())
+    want = {k: v.astype(np.float64) for k, v in TT.read_outputs(alone, str(tmp_path / "alone"), cfg["vocab_size"]).items()}
+    expected = {}
+    for (rid, pos), row in want.items():
+        expected.setdefault(rid, {})[pos] = row
+    before = binding.kernel_launches()["stream_tmap"]
+    for run in range(3):
+        out_dir = str(tmp_path / f"together{run}")
+        replay(runner, together.lines(), out_dir, done=io.StringIO())
+        runner.cache.check()
+        got = TT.read_outputs(together, out_dir, cfg["vocab_size"])
+        assert set(got) == set(want)
+        d_max, where = TT.worst(got, expected)
+        assert d_max <= tols["bfloat16"], f"run {run}: twelve together differ from alone by {d_max:.3e} at {where}"
+    assert binding.kernel_launches()["stream_tmap"] > before
