@@ -80,10 +80,11 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
 }
-// Between a thread's last read of a buffer that the copy engine fills and the arrival that hands it
-// back: the reads are generic-proxy accesses, the next copy an async-proxy write, and the mbarrier
-// alone does not order the one before the other (see gemv_stream.cu, where it was measured).
-__device__ __forceinline__ void stage_read_done() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+// Before a thread copies into a buffer that the consumers have read: their reads are generic-proxy
+// accesses, the copy an async-proxy write, and the mbarrier alone does not order the one before the
+// other (see gemv_stream.cu, where it was measured).  Every lane that issues a copy fences after the
+// wait for the buffer (lane 0's, passed on by __syncwarp) and before its copy.
+__device__ __forceinline__ void stage_is_mine() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CW * 32) : "memory"); }
 
 // One counter per (token, group of heads): every split of that group that saw keys takes a
@@ -206,7 +207,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const unsigned qb = live_items & 1, quse = live_items >> 1;
         auto issue_q = [&]() {
           if (lane == 0) {
-            if (quse > 0) mbar_wait(qempty0 + 8 * qb, (quse - 1) & 1, status, 21);
+            if (quse > 0) {
+              mbar_wait(qempty0 + 8 * qb, (quse - 1) & 1, status, 21);
+              stage_is_mine();
+            }
             mbar_expect_tx(qfull0 + 8 * qb, (unsigned)w.n_rows * HD * 2);
             bulk_copy(q_u + qb * Q_BYTES, q + ((long long)w.t * n_heads + w.head0) * HD,
                       (unsigned)w.n_rows * HD * 2, qfull0 + 8 * qb);
@@ -240,6 +244,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             mbar_expect_tx(full0 + 8 * s, n_valid * BOX_BYTES);
           }
           __syncwarp();
+          stage_is_mine();
           if (valid) {
             const unsigned dst = ring_u + s * STAGE_BYTES + is_v * 8 * GRAN_BYTES + gran * GRAN_BYTES + half * BOX_BYTES;
             tma_load_2d(dst, is_v ? &map_v : &map_k, half * 64, box_row, full0 + 8 * s);
@@ -279,7 +284,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 #pragma unroll
       for (int kk = 0; kk < HD / 16; kk++)
         ldmatrix_x4(qa[kk], q_u + b * Q_BYTES + (lane & 15) * (HD * 2) + (kk * 16 + (lane >> 4) * 8) * 2);
-      stage_read_done();
       __syncwarp();
       if (lane == 0) mbar_arrive(qempty0 + 8 * b);
     }
@@ -382,7 +386,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           mma_bf16(o[d + 1], a, b[2], b[3]);
         }
       }
-      stage_read_done();
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
     }

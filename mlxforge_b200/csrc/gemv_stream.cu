@@ -77,12 +77,14 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// Between a thread's last read of a stage and the arrival that hands the stage back.  The reads are
-// ordinary loads (generic proxy), the copy that overwrites the stage comes from the copy engine
-// (async proxy), and an mbarrier orders accesses within one proxy only: without this fence a lane
-// now and then read the NEXT copy's bytes (weights coded by tile and stage showed it: 16 rows of x,
-// 2048 x 8192, wrong in 595 of 600 launches, 17 of 600 at 16384 x 2048; with the fence 0 of 600).
-__device__ __forceinline__ void stage_read_done() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+// Before the producer copies into a stage that the consumers have read.  Their reads are ordinary loads
+// (generic proxy), the copy comes from the copy engine (async proxy), and an mbarrier orders accesses
+// within one proxy only: the thread that issues the copy puts a proxy fence between its wait for the
+// stage and the copy.  Without it a lane now and then multiplied with the NEXT copy's bytes (weights
+// coded by tile and stage showed it: 16 rows of x, 2048 x 8192, wrong in 595 of 600 launches, 17 of
+// 600 at 16384 x 2048; with the fence 0 of 600, whether the readers fence before they hand the stage
+// back or the producer fences once it has it: the latter is one thread's fence, off the readers' path).
+__device__ __forceinline__ void stage_is_mine() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CW * 32) : "memory"); }
 
 template <int NB, int ROWS, typename OutT>
@@ -127,6 +129,7 @@ stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
           mbar_expect_tx(full, kbytes * (unsigned)nvalid);
         }
         __syncwarp();
+        stage_is_mine();       // every lane that copies: after lane 0's wait, before its own copy
         if (lane < nvalid)
           bulk_copy(ring_u + s * STAGE_BYTES + lane * ROW_BYTES,
                     W + (long long)(n0 + lane) * K + (long long)ks * KT, kbytes, full);
@@ -174,7 +177,6 @@ stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
           mma_bf16(acc[nb], a.z, b.z, a.w, b.w, xv[c][nb].z, xv[c][nb].w);
         }
       }
-      stage_read_done();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars_u + 8 * (STAGES + s));
     }
@@ -270,7 +272,10 @@ stream_tmap_kernel(const __nv_bfloat16* __restrict__ x, const __grid_constant__ 
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         for (int ks = 0; ks < n_ks; ks++, it++) {
           const unsigned s = it % T_STAGES, round = it / T_STAGES;
-          if (round > 0) mbar_wait(bars_u + 8 * (T_STAGES + s), (round - 1) & 1, status, 1);
+          if (round > 0) {
+            mbar_wait(bars_u + 8 * (T_STAGES + s), (round - 1) & 1, status, 1);
+            stage_is_mine();
+          }
           mbar_expect_tx(bars_u + 8 * s, T_STAGE_BYTES);       // rows outside the matrix arrive as zeros
           tma_load_3d(ring_u + s * T_STAGE_BYTES, &map, 0, tile * ROWS, ks * (KSTAGE / 64), bars_u + 8 * s);
         }
@@ -320,7 +325,6 @@ stream_tmap_kernel(const __nv_bfloat16* __restrict__ x, const __grid_constant__ 
           }
         }
       }
-      stage_read_done();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars_u + 8 * (T_STAGES + s));
     }
@@ -421,7 +425,7 @@ int dispatch(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, i
   // Tensor copies for every width of whole 64-column spans; a box that hangs over the end of the
   // matrix along K arrives with zeros there and counts its full size.  (Widths that are not whole
   // stages were once kept off this path because 3 x 128256 x 64 gave wrong rows: that was the
-  // missing fence of stage_read_done(), which shows most where a block has many one-stage tiles.)
+  // missing fence of stage_is_mine(), which shows most where a block has many one-stage tiles.)
   if (K % 64 == 0 && g_stream_tensor_copies) {
     // Six stages of 16 KB, two blocks per SM: under load a copy takes 3 to 4 us to arrive, so an SM
     // has to keep nearly all of its shared memory on the way (four stages: 1.141 ms for a decode step
