@@ -761,3 +761,94 @@ def test_gemm_tcgen05_swiglu(M, I, K):
     eu = 2.0 ** -19 * (np.abs(x).astype(np.float64) @ np.abs(wu).astype(np.float64).T)
     bound = 1.1 * eg * (np.abs(u) + eu) + np.abs(silu) * eu + 2.0 ** -8 * np.abs(want) + 1e-6
     assert np.all(np.abs(host(out) - want) <= bound)
+
+
+def _coded_operands(M, N, K, groups=16):
+    """x rows that each pick one of ``groups`` ranges of K, weights that say which 128 rows and which
+    eighth of K they come from (integers up to 255): every sum is exact in float32, and a tile or a
+    stage taken from elsewhere shows as another value."""
+    import torch
+    k = torch.arange(K, device="cuda")
+    m = torch.arange(M, device="cuda")
+    x = ((k[None, :] * groups // K) == (m[:, None] % groups)).to(torch.bfloat16)
+    n = torch.arange(N, device="cuda")
+    w = (((n[:, None] // 128) % 32) + 32 * (k[None, :] * 8 // K)).to(torch.bfloat16)
+    return x, w
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 3072, 2048), (2048, 2048, 8192), (512, 16384, 2048), (300, 1000, 1536)])
+def test_gemm_tcgen05_is_exact_launch_after_launch(M, N, K):
+    """The many-row product's rings (operands by TMA, two accumulators in tensor memory) under repeated
+    launches with coded operands: exact sums, every launch."""
+    import torch
+    from mlxforge_b200.csrc import ops
+    x, w = _coded_operands(M, N, K)
+    assert ops.gemm_ok(x, w)
+    want = x.double() @ w.double().T
+    out = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    for launch in range(25):
+        out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        ops.gemm_bf16(x, w, out)
+        torch.cuda.synchronize()
+        assert bool((out.double() == want).all()), f"launch {launch}"
+    ops.check_kernel_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 3072, 2048), (64, 2048, 8192), (128, 16384, 2048), (17, 2048, 2048)])
+def test_mid_linear_is_exact_launch_after_launch(M, N, K):
+    """The same for the product of 17 to 128 rows, whose tiles are shared between blocks and reduced by
+    whoever takes a tile's last ticket."""
+    import torch
+    from mlxforge_b200.csrc import ops
+    x, w = _coded_operands(M, N, K)
+    want = x.double() @ w.double().T
+    out = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    scratch = torch.empty(ops.mid_rows_scratch(M), dtype=torch.float32, device="cuda")
+    for launch in range(25):
+        out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        ops.mid_linear(x, w, out, scratch)
+        torch.cuda.synchronize()
+        assert bool((out.double() == want).all()), f"launch {launch}"
+    ops.check_kernel_status()
+
+
+@pytest.mark.parametrize("hd,tcgen05", [(64, True), (128, True), (64, False)])
+def test_prefill_attention_rings_launch_after_launch(hd, tcgen05):
+    """Prefill attention of 2048 tokens with queries of zero (every visible key weighs the same) and values
+    that say which tile of 64 keys they belong to: row p must return the average of the codes of keys
+    0..p, launch after launch; a tile of values read from another turn of the ring moves it by 1 or more."""
+    import torch
+    from mlxforge_b200.csrc import ops
+    T, nh, nkv, page = 2048, 8, 2, 16
+    n_pages = T // page
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    table = torch.randperm(n_pages, generator=gen, device="cuda").to(torch.int32).view(1, n_pages).contiguous()
+    k_pool = torch.randn((n_pages, nkv, page, hd), generator=gen, device="cuda").to(torch.bfloat16)
+    v_pool = torch.empty((n_pages, nkv, page, hd), dtype=torch.bfloat16, device="cuda")
+    key = torch.arange(T, device="cuda")
+    code = (((key // 64) % 7) * 32).to(torch.float32)
+    for h in range(nkv):
+        v_pool[table[0].long(), h] = (code + 8.0 * h).view(n_pages, page, 1).expand(-1, -1, hd).to(torch.bfloat16)
+    q = torch.zeros((T, nh * hd), dtype=torch.bfloat16, device="cuda")
+    heads = (torch.arange(nh, device="cuda") // (nh // nkv)).double()
+    want = (torch.cumsum(code.double(), 0) / (key + 1).double())[:, None, None] + 8.0 * heads[None, :, None]
+    out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device="cuda")
+
+    def i32(v):
+        return torch.tensor([v], dtype=torch.int32, device="cuda")
+
+    ops.set_prefill_tcgen05(tcgen05)
+    try:
+        for launch in range(25):
+            out.fill_(float("nan"))
+            torch.cuda.synchronize()
+            ops.attention_prefill(q, k_pool, v_pool, out, i32(0), i32(T), i32(T), 0, T, table, page, nh, nkv, hd, hd ** -0.5, 0)
+            torch.cuda.synchronize()
+            err = float((out.double().view(T, nh, hd) - want).abs().max())
+            assert err < 0.6, f"launch {launch}: an average is off by {err:.2f}"
+        ops.check_kernel_status()
+    finally:
+        ops.set_prefill_tcgen05(True)
+
