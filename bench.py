@@ -496,6 +496,19 @@ def main() -> int:
                "products_frac": round(gemm_flops / t_gemm / (pk["bf16_tflops"] * 1e12), 4)}
 
     e2e_value, h2d, d2h = decode_e2e(engine, BATCH_, ctx, args.steps, args.warmup)
+    # what the Python host costs at the other batch sizes, and what launching a step before the tokens of
+    # the one before are on the host is worth: the same metric through the entry point
+    e2e_points = {}
+    if not args.skip_points:
+        half = max(8, args.steps // 2)
+        e2e_points["decode_b1"] = round(decode_e2e(engine, 1, ctx, half, args.warmup)[0], 1)
+        e2e_points["decode_b64_ctx1024"] = round(decode_e2e(engine, 64, 1024, half, args.warmup)[0], 1)
+        engine.pipeline = False
+        try:
+            e2e_points["decode_b8_unpipelined"] = round(decode_e2e(engine, BATCH_, ctx, half, args.warmup)[0], 1)
+            e2e_points["decode_b1_unpipelined"] = round(decode_e2e(engine, 1, ctx, half, args.warmup)[0], 1)
+        finally:
+            engine.pipeline = True
 
     line = {
         "metric": f"decode tok/s @ batch {BATCH_} ({shape_name} bf16)", "value": round(value, 1), "unit": "tokens/s",
@@ -520,6 +533,7 @@ def main() -> int:
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
         "point_fracs": point_fracs,
+        "e2e_points": e2e_points,
         "ms_per_step_pieces": {"median": round(statistics.median(pieces), 4), "min": round(min(pieces), 4),
                                "max": round(max(pieces), 4), "pieces": len(pieces)},
     }
