@@ -354,8 +354,9 @@ int launch(const void* x, const void* W, OutT* out, float* scratch, int M, int N
                          N, K, NT, stages, status);
 }
 
-// Units of several spans only where every box lies inside the matrix along K (the few-row product's
-// rule for its 3-D boxes, gemv_stream.cu); other widths take one span per unit through 2-D boxes.
+// Units of several spans where K is whole units (the unit's k-steps are counted from K, so a unit that
+// hangs over would multiply zero-filled spans for nothing); other widths take one span per unit
+// through 2-D boxes.
 template <int MODE, typename OutT>
 int launch_for_width(const void* x, const void* W, OutT* out, float* scratch, int M, int N, int K, int* status,
                      cudaStream_t stream) {
