@@ -527,7 +527,8 @@ def test_mid_linear_swiglu(M, I, K):
 
 @pytest.mark.parametrize("M,N,K", [(16, 2048, 8192), (16, 16384, 2048), (8, 16384, 2048), (12, 16384, 3072), (16, 28672, 4096),
                                    (3, 128256, 64), (16, 50000, 128), (8, 20000, 1536), (13, 2050, 192)])
-def test_stream_linear_reads_a_stage_before_the_next_copy_lands(M, N, K):
+@pytest.mark.parametrize("tensor_copies", [True, False])
+def test_stream_linear_reads_a_stage_before_the_next_copy_lands(M, N, K, tensor_copies):
     """A stage of the ring is read by ordinary loads and overwritten by the copy engine: the reads must be
     done before the stage is handed back.  Weights that say which tile and which quarter of K they come
     from, rows of x that each pick one sixteenth of K, float32 sums of small integers: every output is
@@ -541,15 +542,20 @@ def test_stream_linear_reads_a_stage_before_the_next_copy_lands(M, N, K):
     w = (((n[:, None] // 16) % 64) + 64 * (k[None, :] * 4 // K)).to(torch.bfloat16)        # at most 255: exact in bfloat16
     want = x.double() @ w.double().T
     out = torch.empty((M, N), dtype=torch.float32, device="cuda")
-    for launch in range(40):
-        out.fill_(float("nan"))
-        torch.cuda.synchronize()
-        ops.stream_linear(x, w, out)
-        torch.cuda.synchronize()
-        wrong = (out.double() != want).nonzero()
-        assert wrong.numel() == 0, (f"launch {launch}: {wrong.shape[0]} wrong sums, first at row {int(wrong[0, 0])} column "
-                                    f"{int(wrong[0, 1])}: {float(out[wrong[0, 0], wrong[0, 1]])} for {float(want[wrong[0, 0], wrong[0, 1]])}")
-    ops.check_kernel_status()
+    ops.set_stream_tensor_copies(tensor_copies)      # False: the ring of row-segment copies, which has the same fence
+    try:
+        for launch in range(30):
+            out.fill_(float("nan"))
+            torch.cuda.synchronize()
+            ops.stream_linear(x, w, out)
+            torch.cuda.synchronize()
+            wrong = (out.double() != want).nonzero()
+            assert wrong.numel() == 0, (f"launch {launch}: {wrong.shape[0]} wrong sums, first at row {int(wrong[0, 0])} column "
+                                        f"{int(wrong[0, 1])}: {float(out[wrong[0, 0], wrong[0, 1]])} for "
+                                        f"{float(want[wrong[0, 0], wrong[0, 1]])}")
+        ops.check_kernel_status()
+    finally:
+        ops.set_stream_tensor_copies(True)
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 304, 80), (8, 2048, 2048), (5, 307, 136), (16, 96, 200), (9, 1000, 64),
